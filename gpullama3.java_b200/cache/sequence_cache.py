@@ -16,6 +16,8 @@ sequence (inference/state/LlamaState.java:44-46,61-64 of the reference project).
   still reach (and the pages of the first ``keep_first`` positions, if the need has any);
 * a *slot group* has a fixed size per sequence: ``StateGroup`` owns ``[entry][slot][...shape]``,
   zeroed when a slot is acquired;
+* a block that keeps several things per run (a mixer's cache and state of its own beside it) asks with ``EntryNeeds``,
+  a tuple of named needs: each goes to the group of its kind and the block is handed a dict of views;
 * a *slot* is acquired when a sequence starts and released when it ends; its pages go back to
   the pools and are handed to later sequences without clearing (positions at or beyond a
   sequence's length are never read).
@@ -45,6 +47,16 @@ class StateNeed:
     """Per-sequence state of fixed size, carried from step to step."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class EntryNeeds:
+    """Several things kept by one run of a block, by name: ``parts`` = ((name, need), ...).  Each need is stored by the
+    group of its own kind, next to the same needs of other entries; the run's view is a dict name -> view."""
+    parts: tuple
+
+    def named(self) -> dict:
+        return dict(self.parts)
 
 
 @dataclass(frozen=True)
@@ -228,8 +240,15 @@ class SequenceCache:
         sizes = CacheSizes(self.n_pages, self.max_slots, dtype, self.device, window_slack)
 
         by_need: dict = {}
+        self._entry_parts: dict[int, list[str]] = {}   # entries that keep several named things
         for entry in sorted(needs):
-            by_need.setdefault(needs[entry], []).append(entry)
+            need = needs[entry]
+            if isinstance(need, EntryNeeds):
+                self._entry_parts[entry] = [name for name, _ in need.parts]
+                for name, part in need.parts:
+                    by_need.setdefault(part, []).append((entry, name))
+            else:
+                by_need.setdefault(need, []).append(entry)
         self.paged_groups: list[PagedGroup] = []
         self.slot_groups: list[CacheGroup] = []
         self._entry_group: dict[int, CacheGroup] = {}
@@ -309,6 +328,9 @@ class SequenceCache:
 
     # ---- what mixers see
     def view(self, entry: int):
+        names = self._entry_parts.get(entry)
+        if names is not None:
+            return {name: self._entry_group[(entry, name)].view((entry, name)) for name in names}
         return self._entry_group[entry].view(entry)
 
     def bytes_per_token(self) -> int:

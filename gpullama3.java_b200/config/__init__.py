@@ -6,8 +6,9 @@ from .registry import (Architecture, architecture_of, config_from_dict, load_con
 from .llama import LlamaConfig, RopeScaling
 from .guduzen import GuduzenConfig
 from .pekerax import PekeraxConfig
+from .gatuzen import GatuzenConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "PartSpec", "ScheduleEntry", "default_schedule",
            "read_config_json", "Architecture", "architecture_of", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture", "LlamaConfig",
-           "RopeScaling", "GuduzenConfig", "PekeraxConfig"]
+           "RopeScaling", "GuduzenConfig", "PekeraxConfig", "GatuzenConfig"]

@@ -42,22 +42,26 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: the registered block kind and the parts it is built from, under the names that block's
-    constructor takes.  Nothing else fixes which parts a layer has."""
+    constructor takes.  Nothing else fixes which parts a layer has.  ``args``: further keyword arguments of the
+    block's constructor that are not parts (numbers of the arrangement itself: a factor on what joins the stream)."""
     block: str
     parts: dict[str, PartSpec]
+    args: dict[str, Any] = field(default_factory=dict)
 
     def with_parts(self, **changes: PartSpec) -> "LayerSpec":
-        return LayerSpec(self.block, {**self.parts, **changes})
+        return LayerSpec(self.block, {**self.parts, **changes}, dict(self.args))
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``cache`` names the cache entry the mixer uses; two schedule entries
     with the same ``cache`` share keys and values, and only the one with ``writes_cache`` stores
-    them.  ``cache`` is None for a mixer that keeps nothing."""
+    them.  ``cache`` is None for a mixer that keeps nothing.  ``enters``: the row of the model's table of pass
+    offsets (``ModelConfig.pass_offsets``) that joins the residual stream right before this run; None: nothing does."""
     layer: int
     cache: int | None
     writes_cache: bool = True
+    enters: int | None = None
 
 
 def default_schedule(n_layers: int) -> list[ScheduleEntry]:
@@ -113,6 +117,16 @@ class ModelConfig:
     def embedding_scale(self) -> float:
         """What the embedding rows are multiplied with as they enter the residual stream."""
         return 1.0
+
+    def output_scale(self) -> float:
+        """What the logits are multiplied with as they leave the head."""
+        return 1.0
+
+    def pass_offsets(self) -> int:
+        """Rows of the model's table of pass offsets: learned vectors of the stream's width of which a schedule entry
+        may name one (``ScheduleEntry.enters``) to be added to the residual stream before its run.  0: the model has no
+        such table.  Its parameter path is ``pass_offsets.table``."""
+        return 0
 
     def output_softcap(self) -> float | None:
         """c when the logits leave the head as c * tanh(logits / c); None when they leave as they are."""

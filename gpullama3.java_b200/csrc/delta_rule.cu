@@ -18,6 +18,12 @@
 // The convolution: channel c of token t gets sum_j w[c, j] x[t - (taps - 1) + j, c] followed by SiLU, where inputs
 // before the step's first token come from the slot's state (the last taps - 1 inputs of the sequence, zero at its
 // start); conv_state_update then stores the step's last taps - 1 inputs there.
+//
+// The same scan also runs the recurrences without the delta correction (linear_scan): S <- diag(g) S + k (beta v)^T,
+// o = S^T q + skip v, which is gated linear attention (a decay per key channel, g = sigmoid(.)^(1/tau), beta = 1) and the
+// state-space recurrence with a scalar decay per head (q = C, k = B, g = exp(-exp(A_log) dt), beta = dt = softplus(.),
+// skip = D); linear_scan_prepare makes their rows.  causal_conv is the convolution in its general form: input and output
+// types of their own, an optional bias, SiLU or no activation, and optionally the input added to the result.
 #include "common.cuh"
 
 namespace b200 {
@@ -114,8 +120,47 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, int ld_x, floa
     }
 }
 
+// The convolution in its general form, VEC neighbouring channels of one token per thread.
+template <typename TI, typename TO, int VEC>
+__global__ void causal_conv_kernel(const TI* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ bias,
+                                   const float* __restrict__ state, size_t slot_stride, const int* __restrict__ slots,
+                                   const int* __restrict__ seq_ids, const int* __restrict__ cu_seqlens, TO* __restrict__ out,
+                                   int ld_out, int channels, int taps, int activation, int add_input) {
+    const int t = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c >= channels) return;
+    const int seq = seq_ids[t];
+    const int local = t - cu_seqlens[seq];
+    const float* st = state + (size_t)slots[seq] * slot_stride;   // [taps - 1][channels], oldest first
+    float acc[VEC], own[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;          // how many tokens before t
+        float v[VEC];
+        if (local - back >= 0) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = to_f32<TI>(x[(size_t)(t - back) * ld_x + c + e]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = st[(size_t)(taps - 1 + local - back) * channels + c + e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            acc[e] += w[(size_t)(c + e) * taps + j] * v[e];
+            if (back == 0) own[e] = v[e];
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        if (activation == 1) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+        if (add_input) acc[e] += own[e];
+        out[(size_t)t * ld_out + c + e] = from_f32<TO>(acc[e]);
+    }
+}
+
 // What the scan needs of every token, made by a kernel of its own over all tokens at once (a warp per token and head):
-// one row of 32-bit numbers per (head, token), [q | k | g (each d_pad wide, zeros behind the d_k) | v (d_v) | beta | k . q | fill
+// one row of 32-bit numbers per (head, token), [q | k | g (each d_pad wide, zeros behind the d_k) | v (d_v) | beta | k . q | skip (unused here) | fill
 // to a multiple of 4], q and k of unit length (q also scaled), g = exp(-exp(A_log) softplus(a + dt_bias)),
 // beta = sigmoid(.).  Rows of one head lie token after token, so a chunk of a sequence's tokens is one contiguous piece
 // that the scan brings into shared memory as it is.
@@ -176,6 +221,73 @@ delta_rule_prepare_kernel(PrepareArgs a) {
     }
 }
 
+// The rows of the recurrences without the delta correction, in the layout the scan reads: [q | k | g | v | beta | k . q |
+// skip].  q rows are scaled by q_scale; the decay is exp(-exp(A_log[h]) softplus(z + bias)) (kind 0) or
+// sigmoid(z + bias)^power (kind 1: exp(-softplus(-(z + bias)) power)), per key channel or per head; beta is 1, or the step
+// size softplus(z + bias) of a per-head decay of kind 0 (`step_scales_value`); skip is skip[h] or 0.
+struct LinearPrepareArgs {
+    const void* q;          // [T, ld_q], head kvh of kv_heads at column kvh d_k
+    int ld_q;
+    const void* k;          // [T, ld_k], likewise
+    int ld_k;
+    const void* v;          // [T, ld_v], head h at column h d_v
+    int ld_v;
+    const void* decay;      // [T, ld_decay]: column h d_k + i, or h when there is one decay per head
+    int ld_decay;
+    const float* decay_bias;   // laid out like a row of `decay`, or null
+    const float* a_log;     // [heads], kind 0
+    const float* skip;      // [heads] or null
+    float* rows;            // [heads, T, row]
+    int n_tokens, heads, kv_heads, d_k, d_v, d_pad, row;
+    float q_scale, power;
+    int decay_kind, decay_per_head, step_scales_value;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+linear_scan_prepare_kernel(LinearPrepareArgs a) {
+    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (unit >= (long long)a.n_tokens * a.heads) return;
+    const size_t t = (size_t)(unit / a.heads);
+    const int h = (int)(unit % a.heads), kvh = h / (a.heads / a.kv_heads);
+    const T* qr = (const T*)a.q + t * a.ld_q + (size_t)kvh * a.d_k;
+    const T* kr = (const T*)a.k + t * a.ld_k + (size_t)kvh * a.d_k;
+    const T* vr = (const T*)a.v + t * a.ld_v + (size_t)h * a.d_v;
+    const size_t d_at = a.decay_per_head ? (size_t)h : (size_t)h * a.d_k;
+    const T* dr = (const T*)a.decay + t * a.ld_decay + d_at;
+    const float* br = a.decay_bias ? a.decay_bias + d_at : nullptr;
+    float* out = a.rows + ((size_t)h * a.n_tokens + t) * a.row;
+    const float neg_rate = a.decay_kind == 0 ? -expf(a.a_log[h]) : 0.f;
+    auto decay_of = [&](float z, float& step) {
+        if (a.decay_kind == 0) {
+            step = softplus(z);
+            return expf(neg_rate * step);
+        }
+        step = 1.f;
+        return expf(-softplus(-z) * a.power);
+    };
+    float step_head = 1.f;
+    const float g_head = a.decay_per_head ? decay_of(to_f32<T>(dr[0]) + (br ? br[0] : 0.f), step_head) : 0.f;
+    float qk = 0.f;
+    for (int i = lane; i < a.d_pad; i += 32) {
+        const bool in = i < a.d_k;
+        const float qv = in ? to_f32<T>(qr[i]) * a.q_scale : 0.f, kv = in ? to_f32<T>(kr[i]) : 0.f;
+        qk += qv * kv;
+        out[i] = qv;
+        out[a.d_pad + i] = kv;
+        float unused;
+        out[2 * a.d_pad + i] = !in ? 0.f : a.decay_per_head ? g_head : decay_of(to_f32<T>(dr[i]) + (br ? br[i] : 0.f), unused);
+    }
+    qk = warp_sum(qk);
+    for (int j = lane; j < a.d_v; j += 32) out[3 * a.d_pad + j] = to_f32<T>(vr[j]);
+    if (lane == 0) {
+        out[3 * a.d_pad + a.d_v] = (a.step_scales_value && a.decay_per_head) ? step_head : 1.f;
+        out[3 * a.d_pad + a.d_v + 1] = qk;
+        out[3 * a.d_pad + a.d_v + 2] = a.skip ? a.skip[h] : 0.f;
+    }
+}
+
 struct ScanArgs {
     const float* rows;      // [heads, T, row] as delta_rule_prepare leaves them
     float* state;           // per slot: [heads][d_k][d_v]
@@ -194,7 +306,8 @@ template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatil
 
 // Shared memory holds two chunks of kChunk prepared rows.  While one chunk is walked the next one is on its way.
 // R lanes share a column and hold RPT rows each; a CTA of 128 threads owns 128 / R columns.
-template <int RPT, int R>
+// LINEAR: without the delta correction, u = beta v and the read-out gains skip v.
+template <int RPT, int R, bool LINEAR>
 __global__ void __launch_bounds__(kScanThreads)
 delta_rule_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
@@ -258,8 +371,9 @@ delta_rule_scan_kernel(ScanArgs a) {
                 dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 read += __shfl_xor_sync(0xffffffffu, read, o);
             }
-            const float u = beta * (v - dot);
-            if (live && r == 0) out[(size_t)tt * a.heads * a.d_v] = read + u * kq;
+            const float u = LINEAR ? beta * v : beta * (v - dot);
+            if (live && r == 0)
+                out[(size_t)tt * a.heads * a.d_v] = LINEAR ? read + u * kq + buf[tt * a.row + b_at + 2] * v : read + u * kq;
 #pragma unroll
             for (int i = 0; i < RPT; ++i) S[i] += kp[i * R] * u;
         }
@@ -273,11 +387,11 @@ delta_rule_scan_kernel(ScanArgs a) {
     }
 }
 
-template <int RPT, int R>
+template <int RPT, int R, bool LINEAR>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     constexpr int cols = kScanThreads / R;
     const size_t smem = sizeof(float) * 2 * (size_t)kChunk * a.row;
-    auto kernel = delta_rule_scan_kernel<RPT, R>;
+    auto kernel = delta_rule_scan_kernel<RPT, R, LINEAR>;
     if (smem > 48 * 1024) {
         const int e = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != 0) return e;
@@ -287,14 +401,26 @@ static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     return launch_status();
 }
 
-template <int RPT>
+template <int RPT, bool LINEAR>
 static int launch_scan_lanes(const ScanArgs& a, int lanes, int n_seqs, cudaStream_t stream) {
     switch (lanes) {
-        case 1: return launch_scan<RPT, 1>(a, n_seqs, stream);
-        case 2: return launch_scan<RPT, 2>(a, n_seqs, stream);
-        case 4: return launch_scan<RPT, 4>(a, n_seqs, stream);
-        case 8: return launch_scan<RPT, 8>(a, n_seqs, stream);
-        case 16: return launch_scan<RPT, 16>(a, n_seqs, stream);
+        case 1: return launch_scan<RPT, 1, LINEAR>(a, n_seqs, stream);
+        case 2: return launch_scan<RPT, 2, LINEAR>(a, n_seqs, stream);
+        case 4: return launch_scan<RPT, 4, LINEAR>(a, n_seqs, stream);
+        case 8: return launch_scan<RPT, 8, LINEAR>(a, n_seqs, stream);
+        case 16: return launch_scan<RPT, 16, LINEAR>(a, n_seqs, stream);
+    }
+    return kErrUnsupportedSize;
+}
+
+template <bool LINEAR>
+static int launch_scan_rows(const ScanArgs& a, int rpt, int lanes, int n_seqs, cudaStream_t stream) {
+    switch (rpt) {
+        case 8: return launch_scan_lanes<8, LINEAR>(a, lanes, n_seqs, stream);
+        case 12: return launch_scan_lanes<12, LINEAR>(a, lanes, n_seqs, stream);
+        case 16: return launch_scan_lanes<16, LINEAR>(a, lanes, n_seqs, stream);
+        case 24: return launch_scan_lanes<24, LINEAR>(a, lanes, n_seqs, stream);
+        case 32: return launch_scan_lanes<32, LINEAR>(a, lanes, n_seqs, stream);
     }
     return kErrUnsupportedSize;
 }
@@ -328,6 +454,33 @@ extern "C" int b200_causal_conv_silu(const void* x, int ld_x, const float* w, fl
     return b200::launch_status();
 }
 
+// The general convolution: x [T, >= channels] of `in_dtype`, out of `out_dtype`; `bias` [channels] or null; `activation`
+// 0 none, 1 SiLU; `add_input`: out = x + conv(x) (after the activation).  State as for b200_causal_conv_silu.
+extern "C" int b200_causal_conv(const void* x, int ld_x, int in_dtype, const float* w, const float* bias, float* state,
+                                long long slot_stride, const int* slots, const int* seq_ids, const int* cu_seqlens, void* out,
+                                int ld_out, int out_dtype, int n_tokens, int n_seqs, int channels, int taps, int activation,
+                                int add_input, int update_state, cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return 0;
+    if (taps < 1 || taps > b200::kMaxTaps || (activation != 0 && activation != 1)) return b200::kErrUnsupportedSize;
+    if (n_tokens > 65535 || n_seqs > 65535) return b200::kErrUnsupportedSize;
+    const bool wide = channels % 4 == 0;
+    const dim3 grid(((wide ? channels / 4 : channels) + 127) / 128, n_tokens), grid_u((channels + 127) / 128, n_seqs);
+    B200_DISPATCH_DTYPE(in_dtype, TI,
+        B200_DISPATCH_DTYPE2(out_dtype, TO,
+            if (wide)
+                b200::causal_conv_kernel<TI, TO, 4><<<grid, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                            slots, seq_ids, cu_seqlens, (TO*)out, ld_out, channels,
+                                                                            taps, activation, add_input);
+            else
+                b200::causal_conv_kernel<TI, TO, 1><<<grid, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                            slots, seq_ids, cu_seqlens, (TO*)out, ld_out, channels,
+                                                                            taps, activation, add_input));
+        if (update_state && taps > 1)
+            b200::conv_state_update_kernel<TI><<<grid_u, 128, 0, stream>>>((const TI*)x, ld_x, state, (size_t)slot_stride, slots,
+                                                                          cu_seqlens, channels, taps));
+    return b200::launch_status();
+}
+
 // The rows a thread holds (rows_per_thread: 8, 12, 16, 24 or 32) times the lanes that share a column (a power of two up
 // to 16) must cover d_k; b200_delta_rule_plan picks the pair for a d_k (0 when none fits): the fewest rows beyond d_k,
 // then the fewest rows per thread (shared memory is read once per row and token by every warp).
@@ -352,7 +505,7 @@ extern "C" int b200_delta_rule_plan(int d_k, int* rows_per_thread, int* lanes) {
 extern "C" int b200_delta_rule_row(int d_k, int d_v) {
     int rpt = 0, lanes = 0;
     if (!b200_delta_rule_plan(d_k, &rpt, &lanes)) return 0;
-    return (3 * rpt * lanes + d_v + 2 + 3) / 4 * 4;
+    return (3 * rpt * lanes + d_v + 3 + 3) / 4 * 4;
 }
 
 extern "C" int b200_delta_rule_scan(const void* qkv, int ld_qkv, const void* beta, int ld_beta, const void* decay,
@@ -373,12 +526,30 @@ extern "C" int b200_delta_rule_scan(const void* qkv, int ld_qkv, const void* bet
     B200_DISPATCH_DTYPE(dtype, T,
         b200::delta_rule_prepare_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p));
     b200::ScanArgs a = {scratch, state, (size_t)slot_stride, slots, cu_seqlens, out, n_tokens, heads, d_k, d_v, row};
-    switch (rpt) {
-        case 8: return b200::launch_scan_lanes<8>(a, lanes, n_seqs, stream);
-        case 12: return b200::launch_scan_lanes<12>(a, lanes, n_seqs, stream);
-        case 16: return b200::launch_scan_lanes<16>(a, lanes, n_seqs, stream);
-        case 24: return b200::launch_scan_lanes<24>(a, lanes, n_seqs, stream);
-        case 32: return b200::launch_scan_lanes<32>(a, lanes, n_seqs, stream);
-    }
-    return b200::kErrUnsupportedSize;
+    return b200::launch_scan_rows<false>(a, rpt, lanes, n_seqs, stream);
+}
+
+// The recurrence without the delta correction over a packed step; see LinearPrepareArgs for the operands.  q, k, v and
+// decay share one storage type; state and out as for b200_delta_rule_scan.
+extern "C" int b200_linear_scan(const void* q, int ld_q, const void* k, int ld_k, const void* v, int ld_v, const void* decay,
+                                int ld_decay, const float* decay_bias, const float* a_log, const float* skip, float* state,
+                                long long slot_stride, const int* slots, const int* cu_seqlens, float* out, float* scratch,
+                                int dtype, int n_tokens, int n_seqs, int heads, int kv_heads, int d_k, int d_v, float q_scale,
+                                float power, int decay_kind, int decay_per_head, int step_scales_value, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (heads < 1 || kv_heads < 1 || heads % kv_heads || d_k < 1 || d_v < 1 || n_seqs > 65535 || heads > 65535 || !scratch)
+        return b200::kErrBadArgument;
+    if ((decay_kind != 0 && decay_kind != 1) || (decay_kind == 0 && !a_log)) return b200::kErrBadArgument;
+    int rpt = 0, lanes = 0;
+    if (!b200_delta_rule_plan(d_k, &rpt, &lanes)) return b200::kErrUnsupportedSize;
+    const int row = b200_delta_rule_row(d_k, d_v);
+    if ((uintptr_t)scratch % 16) return b200::kErrBadArgument;
+    b200::LinearPrepareArgs p = {q, ld_q, k, ld_k, v, ld_v, decay, ld_decay, decay_bias, a_log, skip, scratch, n_tokens, heads,
+                                 kv_heads, d_k, d_v, rpt * lanes, row, q_scale, power, decay_kind, decay_per_head ? 1 : 0,
+                                 step_scales_value ? 1 : 0};
+    const long long units = (long long)n_tokens * heads;
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::linear_scan_prepare_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p));
+    b200::ScanArgs a = {scratch, state, (size_t)slot_stride, slots, cu_seqlens, out, n_tokens, heads, d_k, d_v, row};
+    return b200::launch_scan_rows<true>(a, rpt, lanes, n_seqs, stream);
 }

@@ -9,6 +9,13 @@
 //     z <- (1 - lambda) z + lambda other[...]       (optional: mixed with the same element of another layer's rows of the
 //                                                   same token, lambda a number in device memory; 32-bit)
 //     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes)
+//     (z[2i], z[2i+1]) <- turned by position * inv_freq[i]   (optional: rotary position encoding over the row's interleaved
+//                                                   pairs, the angle, its cosine and sine in 32 bits; `mul` then also carries
+//                                                   a factor on cosine and sine)
+// A segment's rows need not lie back to back (`src_stride`: a part of every head of a wider projection; 0 as a stride:
+// every row reads the same numbers, one row shared by all heads) nor be written back to back (`dst_stride`), and a row may
+// fill only some columns of a cache row (`dst_off` columns in, `cache_dim` the cache's row size), so that two segments can
+// make up one key row.
 // A segment's rows go to a dense buffer (queries), or straight into the paged cache at the token's position: as key
 // rows ([page][kv_head][position][d_pad]) or as value rows (transposed, [page][kv_head][d_pad][position]), so that
 // a mixer without rotation needs no other kernel between its projection and attention.
@@ -31,6 +38,10 @@ struct RowSegment {
     int target;       // 0: dst; 1: key rows of the cache; 2: value rows of the cache
     int weight_per_row;  // 1: the weight has n_rows * d entries (one per element of the segment), 0: d (shared by the rows)
     int mix_off;      // column of `other` where this segment's counterpart starts, -1: no mixing
+    int rotate;       // 1: the row's pairs (2i, 2i + 1) are turned by position * inv_freq[i] (d even, no mixing)
+    int src_stride;   // numbers between two rows of the source (-1: d)
+    int dst_stride;   // numbers between two rows written to dst (-1: d_pad)
+    int cache_dim;    // row size of the cache the segment goes into (-1: d_pad); the segment starts dst_off columns in
 };
 struct MixSource {
     const void* other;      // [T][ld_other], the run's storage type
@@ -44,6 +55,7 @@ struct CacheTarget {
     int table_stride;
     void* k_pool;
     void* v_pool;
+    const float* inv_freq;   // for segments that rotate
 };
 struct RowSegments {
     RowSegment seg[kRowSegments];
@@ -58,7 +70,7 @@ __device__ __forceinline__ void head_row(const T* __restrict__ src, int ld_src, 
                                          const float* __restrict__ bias, const float* __restrict__ weight, const RowSegment& g,
                                          int t, int row, int lane, float eps, float whole, const CacheTarget& cache,
                                          const MixSource& mix) {
-    const T* x = src + (size_t)t * ld_src + g.src_off + (size_t)row * g.d;
+    const T* x = src + (size_t)t * ld_src + g.src_off + (size_t)row * (g.src_stride >= 0 ? g.src_stride : g.d);
     const float* b = g.bias_off >= 0 ? bias + g.bias_off + (size_t)row * g.d : nullptr;
     float factor = g.mul;
     if (g.norm == 2) {
@@ -75,18 +87,36 @@ __device__ __forceinline__ void head_row(const T* __restrict__ src, int ld_src, 
     const float* w = g.weight_off >= 0 ? weight + g.weight_off + (g.weight_per_row ? (size_t)row * g.d : 0) : nullptr;
     const T* other = g.mix_off >= 0 ? (const T*)mix.other + (size_t)t * mix.ld_other + g.mix_off + (size_t)row * g.d : nullptr;
     const float lambda = other ? mix.lambda[0] : 0.f;
-    T* o = dst + (size_t)t * ld_dst + g.dst_off + (size_t)row * g.d_pad;
+    T* o = dst + (size_t)t * ld_dst + g.dst_off + (size_t)row * (g.dst_stride >= 0 ? g.dst_stride : g.d_pad);
     size_t step = 1;
     if (g.target != 0) {   // the row's place in the page of this token's position (n_rows = the cache's kv heads)
         const int pos = cache.positions[t];
+        const int dim = g.cache_dim >= 0 ? g.cache_dim : g.d_pad;
         const size_t page = cache.page_table[(size_t)cache.seq_ids[t] * cache.table_stride + pos / kPageTokens];
-        const size_t head = (page * g.n_rows + row) * kPageTokens * g.d_pad;
+        const size_t head = (page * g.n_rows + row) * kPageTokens * dim;
         if (g.target == 1) {
-            o = (T*)cache.k_pool + head + (size_t)(pos % kPageTokens) * g.d_pad;
+            o = (T*)cache.k_pool + head + (size_t)(pos % kPageTokens) * dim + (g.cache_dim >= 0 ? g.dst_off : 0);
         } else {
-            o = (T*)cache.v_pool + head + (pos % kPageTokens);
+            o = (T*)cache.v_pool + head + (size_t)(g.cache_dim >= 0 ? g.dst_off : 0) * kPageTokens + (pos % kPageTokens);
             step = kPageTokens;
         }
+    }
+    if (g.rotate) {
+        const float pos = (float)cache.positions[t];
+        for (int i = lane; 2 * i < g.d_pad; i += 32) {
+            float z0 = 0.f, z1 = 0.f;
+            if (2 * i + 1 < g.d) {
+                const float u = (to_f32<T>(x[2 * i]) + (b ? b[2 * i] : 0.f)) * factor * (w ? w[2 * i] : 1.f);
+                const float v = (to_f32<T>(x[2 * i + 1]) + (b ? b[2 * i + 1] : 0.f)) * factor * (w ? w[2 * i + 1] : 1.f);
+                float sn, cs;
+                sincosf(pos * cache.inv_freq[i], &sn, &cs);
+                z0 = u * cs - v * sn;
+                z1 = v * cs + u * sn;
+            }
+            o[(size_t)(2 * i) * step] = from_f32<T>(z0);
+            if (2 * i + 1 < g.d_pad) o[(size_t)(2 * i + 1) * step] = from_f32<T>(z1);
+        }
+        return;
     }
     for (int e = lane; e < g.d_pad; e += 32) {
         float z = 0.f;
@@ -156,20 +186,20 @@ head_rows_token_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ ds
 
 }  // namespace b200
 
-// `segments`: n_segments records of twelve 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
-// weight_off, mul as float bits, target, weight_per_row, mix_off), read on the host.  Segments with a cache target need positions, seq_ids,
+// `segments`: n_segments records of sixteen 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
+// weight_off, mul as float bits, target, weight_per_row, mix_off, rotate, src_stride, dst_stride, cache_dim), read on the host.  Segments with a cache target need positions, seq_ids,
 // page_table and the pools; their n_rows is the number of kv heads of the cache entry and d_pad its head size.
 extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst, int dtype, const float* bias,
                               const float* weight, const int* segments, int n_segments, int n_tokens, float eps,
                               const int* positions, const int* seq_ids, const int* page_table, int table_stride,
                               void* k_pool, void* v_pool, const void* other, int ld_other, const float* lambda,
-                              cudaStream_t stream) {
+                              const float* inv_freq, cudaStream_t stream) {
     if (n_tokens <= 0 || n_segments <= 0) return 0;
     if (n_segments > b200::kRowSegments) return b200::kErrBadArgument;
     b200::RowSegments segs = {};
     segs.n = n_segments;
     for (int i = 0; i < n_segments; ++i) {
-        const int* p = segments + 12 * i;
+        const int* p = segments + 16 * i;
         b200::RowSegment& g = segs.seg[i];
         g.src_off = p[0]; g.n_rows = p[1]; g.d = p[2]; g.dst_off = p[3]; g.d_pad = p[4];
         g.bias_off = p[5]; g.norm = p[6]; g.weight_off = p[7];
@@ -179,6 +209,9 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
         g.target = p[9];
         g.weight_per_row = p[10];
         g.mix_off = p[11];
+        g.rotate = p[12]; g.src_stride = p[13]; g.dst_stride = p[14]; g.cache_dim = p[15];
+        if (g.rotate && (!inv_freq || !positions || g.d % 2 || g.mix_off >= 0)) return b200::kErrBadArgument;
+        if (g.cache_dim >= 0 && (g.target == 0 || g.dst_off < 0 || g.dst_off + g.d_pad > g.cache_dim)) return b200::kErrBadArgument;
         if (g.norm < 0 || g.norm > 2) return b200::kErrBadArgument;
         if (g.mix_off >= 0 && (other == nullptr || lambda == nullptr)) return b200::kErrBadArgument;
         if (g.target < 0 || g.target > 2) return b200::kErrBadArgument;
@@ -192,7 +225,7 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     const int per_cta = b200::kRowThreads / 32;
     dim3 grid(n_tokens, (segs.total_rows + per_cta - 1) / per_cta);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
-    const b200::CacheTarget cache = {positions, seq_ids, page_table, table_stride, k_pool, v_pool};
+    const b200::CacheTarget cache = {positions, seq_ids, page_table, table_stride, k_pool, v_pool, inv_freq};
     const b200::MixSource mix = {other, ld_other, lambda};
     bool per_token = false;
     for (int i = 0; i < n_segments; ++i) per_token = per_token || segs.seg[i].norm == 2;

@@ -477,6 +477,27 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
 
 }  // namespace b200
 
+namespace b200 {
+// Routing without a router: row tokens[t] of a table names the token's experts, all weighted alike.
+__global__ void moe_table_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int* __restrict__ chosen,
+                                       float* __restrict__ weights, int n, int top, int n_experts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = table[(size_t)tokens[i / top] * top + i % top];
+    chosen[i] = min(max(e, 0), n_experts - 1);   // (a table entry outside the experts cannot index past them)
+    weights[i] = 1.0f / (float)top;
+}
+}  // namespace b200
+
+extern "C" int b200_moe_table_route(const int* tokens, const int* table, int* chosen, float* weights, int n_tokens, int top,
+                                    int n_experts, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || n_experts < 1) return b200::kErrBadArgument;
+    const int n = n_tokens * top;
+    b200::moe_table_route_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, table, chosen, weights, n, top, n_experts);
+    return b200::launch_status();
+}
+
 extern "C" int b200_moe_route(const void* h, int ld_h, int dtype, const float* router, int* chosen, float* weights,
                               float* scores, int n_tokens, int width, int n_experts, int n_groups, int keep_groups, int top,
                               float norm_eps, cudaStream_t stream) {

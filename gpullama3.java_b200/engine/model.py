@@ -14,7 +14,7 @@ import torch
 from ..cache.sequence_cache import SequenceCache
 from ..config.base import ConfigError, ModelConfig, ScheduleEntry
 from ..parts.base import Block, Part, StepContext, all_parts, build_block, build_part
-from ..parts.embedding import OutputHead, TokenEmbedding
+from ..parts.embedding import OutputHead, PassOffsets, TokenEmbedding
 from ..parts.streams import close_streams_norm, open_streams
 from ..weights.loader import ParamSpec, load_checkpoint_tensors
 from ..weights.safetensors_io import WeightError
@@ -30,7 +30,10 @@ class CausalLM:
         self.final_norm = build_part(config.final_norm())
         self.head = OutputHead(config.vocab_size, config.hidden_size,
                                tied_to=self.embedding if config.tie_word_embeddings else None,
-                               softcap=config.output_softcap())
+                               softcap=config.output_softcap(), scale=config.output_scale())
+        # vectors that join the residual stream before certain runs of the schedule (a looped run of layers tells its
+        # passes apart this way); a model without any has no such part
+        self.pass_offsets = PassOffsets(config.pass_offsets(), config.hidden_size) if config.pass_offsets() else None
         # blocks that keep several residual streams per token say how many; all blocks of a model agree
         counts = {getattr(b, "streams", None) for b in self.blocks}
         if len(counts) > 1:
@@ -47,6 +50,9 @@ class CausalLM:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
+            if e.enters is not None and not (self.pass_offsets is not None and 0 <= e.enters < self.pass_offsets.rows):
+                raise ConfigError(f"schedule entry {i} names pass offset {e.enters}, the model has "
+                                  f"{self.pass_offsets.rows if self.pass_offsets is not None else 0}")
             need = self.blocks[e.layer].cache_need()
             if need is None:
                 if e.cache is not None:
@@ -84,7 +90,11 @@ class CausalLM:
         parts: dict[str, Part] = {"embedding": self.embedding}
         parts.update(all_parts(self.embedding, "embedding."))
         for i, b in enumerate(self.blocks):
+            if b.parameters():      # a block with parameters of its own (``layers.3.<name>``), beside those of its parts
+                parts[f"layers.{i}"] = b
             parts.update(all_parts(b, f"layers.{i}."))
+        if self.pass_offsets is not None:
+            parts["pass_offsets"] = self.pass_offsets
         for name, part in (("final_norm", self.final_norm), ("head", self.head)):
             parts[name] = part
             parts.update(all_parts(part, name + "."))
@@ -161,9 +171,15 @@ class CausalLM:
             view = cache.view(entry.cache) if entry.cache is not None else None
             block = self.blocks[entry.layer]
             mark = ws.mark() if ws is not None else 0
+            if entry.enters is not None and handed is None:
+                self.pass_offsets.add_to(residual, entry.enters)
             if block.takes_scaled_rows(ctx):
                 nxt = self.blocks[self.schedule[k + 1].layer] if k + 1 < len(self.schedule) else None
                 then = nxt.first_norm() if nxt is not None and nxt.takes_scaled_rows(ctx) else None
+                if then is not None and self.schedule[k + 1].enters is not None:
+                    # the next run's offset joins the stream before that run's norm: a block that can add it in its own
+                    # last kernel is handed the row, any other block leaves the norm to the next one
+                    then = block.with_offset(then, self.pass_offsets.row(self.schedule[k + 1].enters))
                 handed = block.forward(residual, ctx, view, entry.writes_cache, x_in=handed, then_norm=then)
             else:
                 block.forward(residual, ctx, view, entry.writes_cache)

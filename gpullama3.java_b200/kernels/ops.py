@@ -84,10 +84,23 @@ _SIGNATURES = {
                                       c_int, c_int, c_float]),
     "b200_head_rows": ("head_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                      c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                     c_void_p]),
+                                     c_void_p, c_void_p]),
     "b200_softcap_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
     "b200_gated_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                           c_float, c_int]),
+                                           c_float, c_int, c_int, c_int]),
+    "b200_gate_rows": ("elementwise", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "b200_scale_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
+    "b200_group_rmsnorm": ("sandwich", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float]),
+    "b200_sandwich_step": ("sandwich", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                        c_int, c_int, c_float]),
+    "b200_add_row": ("sandwich", [c_void_p, c_void_p, c_int, c_int]),
+    "b200_causal_conv": ("delta_rule", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int]),
+    "b200_linear_scan": ("delta_rule", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int]),
+    "b200_moe_table_route": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_layernorm": ("norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float]),
     "b200_causal_conv_silu": ("delta_rule", [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
@@ -817,29 +830,36 @@ def streams_step(x: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, y: tor
 TO_ROWS, TO_CACHE_KEYS, TO_CACHE_VALUES = 0, 1, 2
 
 
-ROW_WORDS = 12   # 32-bit words of one segment record (head_rows.cu)
+ROW_WORDS = 16   # 32-bit words of one segment record (head_rows.cu)
 
 
 def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int | None = None, bias_off: int = -1,
                      norm: bool | int = False, weight_off: int = -1, mul: float = 1.0, target: int = TO_ROWS,
-                     weight_per_row: bool = False, mix_off: int = -1) -> list[int]:
+                     weight_per_row: bool = False, mix_off: int = -1, rotate: bool = False, src_stride: int = -1,
+                     dst_stride: int = -1, cache_dim: int = -1) -> list[int]:
     """One segment of ``head_rows``: ``n_rows`` rows of ``d`` numbers from column ``src_off`` on, each (+ bias)
     (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on, or with
     ``target`` TO_CACHE_KEYS / TO_CACHE_VALUES into the cache page of the token's position (``n_rows`` = the cache
     entry's kv heads, ``d_pad`` its head size).  ``norm``: True / 1 per row, 2 over all rows of the segment at once
     (the weight then usually has an entry per element: ``weight_per_row``).  ``mix_off``: the column of ``head_rows``'s
-    ``other`` rows this segment is mixed with."""
+    ``other`` rows this segment is mixed with.  ``rotate``: the row's interleaved pairs (2i, 2i + 1) are turned by the
+    token's position times ``head_rows``'s ``rotary`` frequencies (``mul`` then also carries a factor on cosine and sine).
+    ``src_stride`` / ``dst_stride``: numbers between two rows read / written when they do not lie back to back (a source
+    stride of 0: all rows read the same numbers).  ``cache_dim``: the row size of the cache, when the segment fills only
+    the ``d_pad`` columns from ``dst_off`` on of every cache row."""
     import struct
 
     return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, int(norm), weight_off,
-            struct.unpack("<i", struct.pack("<f", float(mul)))[0], target, 1 if weight_per_row else 0, mix_off]
+            struct.unpack("<i", struct.pack("<f", float(mul)))[0], target, 1 if weight_per_row else 0, mix_off,
+            1 if rotate else 0, src_stride, dst_stride, cache_dim]
 
 
 def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
-              weight: torch.Tensor | None = None, cache=None, mix=None) -> None:
+              weight: torch.Tensor | None = None, cache=None, mix=None, rotary=None) -> None:
     """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments).  ``cache``: (positions,
     seq_ids, page_table, k_pool, v_pool) for segments that go into the paged cache; ``dst`` may be None when all do.
-    ``mix``: (other [T, >= ...] of src's dtype, lambda float32 [1]) for segments with a ``mix_off``."""
+    ``mix``: (other [T, >= ...] of src's dtype, lambda float32 [1]) for segments with a ``mix_off``.  ``rotary``:
+    (positions int32 [T], inverse frequencies float32 [>= d / 2]) for segments that rotate."""
     _dev(src, dst, bias, weight)
     assert src.stride(1) == 1
     assert dst is None or (src.dtype == dst.dtype and dst.stride(1) == 1 and src.shape[0] == dst.shape[0])
@@ -857,12 +877,19 @@ def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float 
         _dev(other, lam)
         assert other.dtype == src.dtype and other.stride(1) == 1 and other.shape[0] == src.shape[0]
         assert lam.dtype == torch.float32 and lam.numel() == 1
+    inv_freq = None
+    if rotary is not None:
+        rot_pos, inv_freq = rotary
+        _dev(rot_pos, inv_freq)
+        assert rot_pos.dtype == torch.int32 and inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
+        assert pos is None or pos.data_ptr() == rot_pos.data_ptr()
+        pos = rot_pos
     ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_head_rows")(src.data_ptr(), src.stride(0), ptr(dst), dst.stride(0) if dst is not None else 0,
                                  dtype_code(src.dtype), ptr(bias), ptr(weight), ctypes.addressof(segments),
                                  len(segments) // ROW_WORDS, src.shape[0], float(eps), ptr(pos), ptr(seq), ptr(table),
                                  table.shape[1] if table is not None else 0, ptr(k_pool), ptr(v_pool), ptr(other),
-                                 other.stride(0) if other is not None else 0, ptr(lam), _stream()), "head_rows")
+                                 other.stride(0) if other is not None else 0, ptr(lam), ptr(inv_freq), _stream()), "head_rows")
 
 
 def head_row_segments(*segments: list[int]):
@@ -883,16 +910,77 @@ GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
 
 
 def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, d: int,
-                  eps: float, activation: str = "sigmoid") -> None:
+                  eps: float, activation: str = "sigmoid", gate_first: bool = False) -> None:
     """Per (token, head) row of float32 x [T, n_heads d]: x / sqrt(mean(x^2) + eps) * weight[d] * act(gate), act the
-    sigmoid or SiLU."""
+    sigmoid or SiLU.  ``gate_first``: the row is multiplied by act(gate) first and the norm runs over the gated row.
+    A weight of n_heads * d numbers gives every row weights of its own (the rows are then any equal parts of x's rows)."""
     _dev(x, weight, gate, out)
     assert x.dtype == weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
-    assert x.shape[1] == n_heads * d == out.shape[1] and gate.shape[1] >= n_heads * d and weight.numel() == d
-    assert gate.dtype == out.dtype
+    assert x.shape[1] == n_heads * d == out.shape[1] and gate.shape[1] >= n_heads * d and weight.numel() in (d, n_heads * d)
+    assert gate.dtype == out.dtype and weight.is_contiguous()
+    per_row = weight.numel() != d
     _check(_fn("b200_gated_rmsnorm")(x.data_ptr(), weight.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(),
                                      dtype_code(out.dtype), x.shape[0], n_heads, d, float(eps),
-                                     GATE_ACTIVATIONS[activation], _stream()), "gated_rmsnorm")
+                                     GATE_ACTIVATIONS[activation], 1 if gate_first else 0, 1 if per_row else 0, _stream()),
+           "gated_rmsnorm")
+
+
+def gate_rows(x: torch.Tensor, gate: torch.Tensor, activation: str = "sigmoid") -> None:
+    """x[t, :] <- x[t, :] * act(gate[t, :x.shape[1]]) in place, act the sigmoid or SiLU, evaluated in 32 bits."""
+    _dev(x, gate)
+    assert x.dtype == gate.dtype and x.stride(1) == 1 and gate.stride(1) == 1
+    assert gate.shape[0] == x.shape[0] and gate.shape[1] >= x.shape[1]
+    _check(_fn("b200_gate_rows")(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), dtype_code(x.dtype), x.shape[0],
+                                 x.shape[1], GATE_ACTIVATIONS[activation], _stream()), "gate_rows")
+
+
+def scale_rows(logits: torch.Tensor, scale: float) -> None:
+    """logits <- logits * scale, in place (float32)."""
+    _dev(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _check(_fn("b200_scale_rows")(logits.data_ptr(), logits.numel(), float(scale), _stream()), "scale_rows")
+
+
+# --------------------------------------------------------------------------- norms in groups, and a block that norms both ways
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, groups: int,
+                  rows: torch.Tensor | None = None) -> None:
+    """out[r] = weight * x[rows[r]] / rms, every row cut into ``groups`` equal consecutive parts that are each divided by
+    their own sqrt(mean(part^2) + eps).  x and weight float32."""
+    _dev(x, weight, out, rows)
+    assert x.dtype == weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and weight.is_contiguous()
+    n_rows, dim = out.shape
+    assert x.shape[1] == dim and weight.numel() == dim
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    _check(_fn("b200_group_rmsnorm")(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                     rows.data_ptr() if rows is not None else None, n_rows, dim, int(groups), float(eps),
+                                     _stream()), "group_rmsnorm")
+
+
+def sandwich_step(y: torch.Tensor, weight: torch.Tensor, mult: float, x: torch.Tensor, eps: float, groups: int, *,
+                  offset: torch.Tensor | None = None, next_weight: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> None:
+    """x <- x + mult * (weight * y / rms_groups(y)) (+ offset); y <- 0; and, with ``next_weight`` and ``out``,
+    out = next_weight * x / rms_groups(x) of the updated rows.  x, y [T, dim] and the weights float32."""
+    _dev(y, weight, x, offset, next_weight, out)
+    assert x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+    assert x.shape == y.shape and weight.numel() == x.shape[1] and weight.is_contiguous()
+    assert offset is None or (offset.dtype == torch.float32 and offset.is_contiguous() and offset.numel() == x.shape[1])
+    assert (next_weight is None) == (out is None)
+    if out is not None:
+        assert next_weight.dtype == torch.float32 and next_weight.is_contiguous() and next_weight.numel() == x.shape[1]
+        assert out.is_contiguous() and out.shape == x.shape
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(_fn("b200_sandwich_step")(y.data_ptr(), weight.data_ptr(), float(mult), x.data_ptr(), ptr(offset), ptr(next_weight),
+                                     ptr(out), dtype_code(out.dtype) if out is not None else F32, x.shape[0], x.shape[1],
+                                     int(groups), float(eps), _stream()), "sandwich_step")
+
+
+def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
+    """x[t] += row for every row t of float32 x [T, dim]."""
+    _dev(x, row)
+    assert x.dtype == row.dtype == torch.float32 and x.is_contiguous() and row.is_contiguous() and row.numel() == x.shape[1]
+    _check(_fn("b200_add_row")(x.data_ptr(), row.data_ptr(), x.shape[0], x.shape[1], _stream()), "add_row")
 
 
 # --------------------------------------------------------------------------- short convolution and the delta rule
@@ -914,6 +1002,65 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor,
                                         slots.data_ptr(), seq_ids.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
                                         out.stride(0), dtype_code(x.dtype), x.shape[0], slots.numel(), channels, taps,
                                         1 if update_state else 0, _stream()), "causal_conv_silu")
+
+
+CONV_ACTIVATIONS = {None: 0, "silu": 1}
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, seq_ids: torch.Tensor,
+                cu_seqlens: torch.Tensor, out: torch.Tensor, channels: int, *, bias: torch.Tensor | None = None,
+                activation: str | None = None, add_input: bool = False, update_state: bool = True) -> None:
+    """The short causal convolution in its general form: out[t, c] = act(bias[c] + sum_j weight[c, j] x[t - (taps - 1) + j, c])
+    (+ x[t, c] with ``add_input``) per sequence of the packed step; x and out may differ in type.  State as for
+    ``causal_conv_silu``: float32 [slots, >= (taps - 1) * channels], the sequence's last taps - 1 inputs, oldest first."""
+    _dev(x, weight, state, slots, seq_ids, cu_seqlens, out, bias)
+    taps = weight.shape[1]
+    assert weight.dtype == state.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == channels
+    assert x.stride(1) == 1 and out.stride(1) == 1 and state.stride(1) == 1 and x.shape[0] == out.shape[0]
+    assert x.shape[1] >= channels and out.shape[1] >= channels and state.shape[1] >= (taps - 1) * channels
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == channels)
+    _check(_fn("b200_causal_conv")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), weight.data_ptr(),
+                                   bias.data_ptr() if bias is not None else None, state.data_ptr(), state.stride(0),
+                                   slots.data_ptr(), seq_ids.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), out.stride(0),
+                                   dtype_code(out.dtype), x.shape[0], slots.numel(), channels, taps,
+                                   CONV_ACTIVATIONS[activation], 1 if add_input else 0, 1 if update_state else 0, _stream()),
+           "causal_conv")
+
+
+DECAY_SOFTPLUS_RATE, DECAY_SIGMOID_POWER = 0, 1
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                slots: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, d_k: int,
+                d_v: int, *, decay_kind: int, decay_per_head: bool = False, decay_bias: torch.Tensor | None = None,
+                a_log: torch.Tensor | None = None, power: float = 1.0, q_scale: float = 1.0,
+                step_scales_value: bool = False, skip: torch.Tensor | None = None, alloc=None) -> None:
+    """The recurrence S <- diag(g) S + k (beta v)^T, o = S^T q + skip v per head over a packed step (no delta correction).
+    q, k [T, >= kv_heads d_k] (head h reads head h // (heads // kv_heads)), v [T, >= heads d_v], decay [T, >= heads d_k]
+    (or [T, >= heads] with ``decay_per_head``) before its bias and activation, all of one type; g =
+    exp(-exp(a_log[h]) softplus(decay + bias)) (``DECAY_SOFTPLUS_RATE``) or sigmoid(decay + bias)^power
+    (``DECAY_SIGMOID_POWER``); beta = 1, or the step size softplus(decay + bias) with ``step_scales_value``.  state float32
+    [slots, >= heads d_k d_v], updated in place; out float32 [T, heads d_v]; everything but the operands' storage is 32-bit."""
+    _dev(q, k, v, decay, state, slots, cu_seqlens, out, decay_bias, a_log, skip)
+    assert q.dtype == k.dtype == v.dtype == decay.dtype and q.stride(1) == k.stride(1) == v.stride(1) == decay.stride(1) == 1
+    assert state.dtype == out.dtype == torch.float32 and out.is_contiguous() and state.stride(1) == 1
+    n_decay = heads if decay_per_head else heads * d_k
+    assert q.shape[1] >= kv_heads * d_k and k.shape[1] >= kv_heads * d_k and v.shape[1] >= heads * d_v and decay.shape[1] >= n_decay
+    for t, n in ((decay_bias, n_decay), (a_log, heads), (skip, heads)):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
+    assert decay_kind != DECAY_SOFTPLUS_RATE or a_log is not None
+    assert not step_scales_value or (decay_per_head and decay_kind == DECAY_SOFTPLUS_RATE)
+    assert state.shape[1] >= heads * d_k * d_v and out.shape[1] == heads * d_v and out.shape[0] == q.shape[0]
+    lib = library("delta_rule")
+    shape = (heads, q.shape[0], int(lib.b200_delta_rule_row(c_int(d_k), c_int(d_v))))
+    scratch = alloc(shape, torch.float32) if alloc is not None else torch.empty(shape, dtype=torch.float32, device=q.device)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(_fn("b200_linear_scan")(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                   decay.data_ptr(), decay.stride(0), ptr(decay_bias), ptr(a_log), ptr(skip), state.data_ptr(),
+                                   state.stride(0), slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                   dtype_code(q.dtype), q.shape[0], slots.numel(), heads, kv_heads, d_k, d_v, float(q_scale),
+                                   float(power), int(decay_kind), 1 if decay_per_head else 0, 1 if step_scales_value else 0,
+                                   _stream()), "linear_scan")
 
 
 def delta_rule_supported(d_k: int) -> bool:
@@ -967,6 +1114,18 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weigh
     _check(_fn("b200_moe_route")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), router.data_ptr(), chosen.data_ptr(),
                                  weights.data_ptr(), scores.data_ptr() if scores is not None else None, T, width, E,
                                  int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps), _stream()), "moe_route")
+
+
+def moe_table_route(tokens: torch.Tensor, table: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+                    n_experts: int) -> None:
+    """Routing by token id: chosen[t] = table[tokens[t]] (int32 [vocab, top]) and every weight 1 / top."""
+    _dev(tokens, table, chosen, weights)
+    T, top = chosen.shape
+    assert tokens.dtype == table.dtype == chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    assert table.is_contiguous() and chosen.is_contiguous() and weights.is_contiguous() and table.shape[1] == top
+    assert tokens.numel() == T and weights.shape == chosen.shape
+    _check(_fn("b200_moe_table_route")(tokens.data_ptr(), table.data_ptr(), chosen.data_ptr(), weights.data_ptr(), T, top,
+                                       int(n_experts), _stream()), "moe_table_route")
 
 
 def moe_rows_takes(k: int, dtype: torch.dtype) -> bool:

@@ -14,10 +14,14 @@ from .latent_attention import LatentAttention
 from .delta_rule import ChannelDeltaRule, HeadDeltaRule
 from .norm import LayerNorm
 from .routed_feed_forward import RoutedFeedForward
+from .linear_recurrence import GatedLinearAttention, StateSpaceDuality
+from .sandwich import SandwichBlock
+from .position import YarnRotaryPositionEncoding
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PartRegistryError", "PositionEncoding", "ScaledRows",
            "StepContext", "all_parts", "build_block", "build_part", "register_block", "register_feed_forward",
            "register_mixer", "register_norm", "register_part", "register_position_encoding", "registered", "unregister", "Linear", "RMSNorm", "NoPositionEncoding",
            "RotaryPositionEncoding", "llama3_inverse_frequencies", "GroupedQueryAttention", "SwiGLUFeedForward",
            "PreNormBlock", "OutputHead", "TokenEmbedding", "ConnectedBlock", "StreamConnection", "LatentAttention",
-           "ChannelDeltaRule", "HeadDeltaRule", "LayerNorm", "RoutedFeedForward"]
+           "ChannelDeltaRule", "HeadDeltaRule", "LayerNorm", "RoutedFeedForward", "GatedLinearAttention",
+           "StateSpaceDuality", "SandwichBlock", "YarnRotaryPositionEncoding"]

@@ -197,6 +197,12 @@ class Block(Part):
         """The norm the block applies to the residual stream before anything else, if it starts that way."""
         return None
 
+    def with_offset(self, then_norm, row: torch.Tensor):
+        """``then_norm`` (the next block's first norm) when a vector ``row`` joins the residual stream between this
+        block and the next: what this block wants as ``then_norm`` so that its last kernel adds the row before it
+        norms, or None when it cannot (the model then adds the row and the next block norms for itself)."""
+        return None
+
 
 def all_parts(root: Part, prefix: str = "") -> dict[str, Part]:
     """Every part below ``root`` by dotted path (``mixer``, ``mixer.position``), parents before children."""
@@ -284,7 +290,7 @@ def build_block(spec) -> Block:
     """The block of a ``LayerSpec``: its registered class, given the layer's built parts by name."""
     cls = _registered_class("block", spec.block)
     try:
-        return cls(**{name: build_part(p) for name, p in spec.parts.items()})
+        return cls(**{name: build_part(p) for name, p in spec.parts.items()}, **dict(getattr(spec, "args", None) or {}))
     except TypeError as e:
         raise PartRegistryError(f"block kind {spec.block!r} does not take the parts "
                                 f"{sorted(spec.parts)}: {e}") from e

@@ -43,10 +43,11 @@ class OutputHead(Part):
     pad_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None,
-                 softcap: float | None = None):
-        """``softcap`` c: logits leave as c * tanh(logits / c)."""
+                 softcap: float | None = None, scale: float = 1.0):
+        """``scale``: what the logits are multiplied with; ``softcap`` c: they then leave as c * tanh(logits / c)."""
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to
         self.softcap = float(softcap) if softcap else None
+        self.scale = float(scale)
         self.linear: Linear | None = None
 
     def parameters(self):
@@ -62,6 +63,31 @@ class OutputHead(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: normalised rows [R, hidden] -> float32 logits [R, vocab]."""
         logits = self.linear.store(x, torch.float32)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
         if self.softcap is not None:
             ops.softcap_rows(logits, self.softcap)
         return logits
+
+
+class PassOffsets(Part):
+    """A table of learned vectors of the residual stream's width; row t joins the stream (x <- x + table[t]) where the
+    schedule says so: before the t-th pass through a run of layers that is repeated with the same weights."""
+    graph_safe = True
+    pad_safe = True
+
+    def __init__(self, rows: int, hidden_size: int):
+        self.rows, self.hidden_size = int(rows), int(hidden_size)
+        self.table: torch.Tensor | None = None
+
+    def parameters(self):
+        return {"table": ParamSpec((self.rows, self.hidden_size))}
+
+    def load(self, tensors, dtype, device):
+        self.table = tensors["table"].to(device=device, dtype=torch.float32).contiguous()
+
+    def row(self, t: int) -> torch.Tensor:
+        return self.table[t]
+
+    def add_to(self, residual: torch.Tensor, t: int) -> None:
+        ops.add_row(residual, self.table[t])

@@ -87,6 +87,59 @@ class RotaryPositionEncoding(PositionEncoding):
         return table
 
 
+def yarn_inverse_frequencies(dims: int, base: float, factor: float, original: float, fast: float, slow: float,
+                             min_ramp_width: float = 0.001) -> list[float]:
+    """f_i = base^(-2i/dims), slowed by ``factor`` where a pair turns fewer than ``slow`` times over ``original`` positions,
+    kept where it turns more than ``fast`` times, blended linearly in the pair index between the two: with
+    pair(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), dims - 1)
+    and r_i = clamp((i - lo) / max(hi - lo, min_ramp_width), 0, 1), the frequency is f_i / factor * r_i + f_i (1 - r_i).
+    Evaluated in double precision."""
+    def pair(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo, hi = max(math.floor(pair(fast)), 0), min(math.ceil(pair(slow)), dims - 1)
+    out = []
+    for i in range(dims // 2):
+        f = base ** (-2.0 * i / dims)
+        r = min(max((i - lo) / max(hi - lo, min_ramp_width), 0.0), 1.0)
+        out.append(f / factor * r + f * (1.0 - r))
+    return out
+
+
+class YarnRotaryPositionEncoding(PositionEncoding):
+    """Rotary encoding over interleaved pairs with frequencies stretched for contexts longer than the ``original`` one
+    (``yarn_inverse_frequencies``); cosine and sine are multiplied by ``magnitude`` = magnitude_slope ln(factor) + 1.
+    Without ``factor`` (or with 1) it is the plain rotary encoding of base ``base``."""
+    graph_safe = True
+    pad_safe = True
+
+    def __init__(self, rotary_dim: int, base: float, factor: float | None = None, original: float | None = None,
+                 fast: float = 32.0, slow: float = 1.0, magnitude_slope: float = 0.1, min_ramp_width: float = 0.001):
+        self.rotary_dim, self.pairing, self.base = int(rotary_dim), PAIRING_CODES["interleaved"], float(base)
+        if self.rotary_dim % 2 or self.rotary_dim < 2:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even and positive")
+        self.factor = float(factor) if factor else 1.0
+        if self.factor != 1.0 and not original:
+            raise ValueError("stretched rotary frequencies need the original context length")
+        self.original, self.fast, self.slow = float(original or 0.0), float(fast), float(slow)
+        self.min_ramp_width = float(min_ramp_width)
+        self.magnitude = float(magnitude_slope) * math.log(self.factor) + 1.0
+        self._inv_freq: dict = {}
+
+    def frequencies(self) -> list[float]:
+        if self.factor == 1.0:
+            return [self.base ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)]
+        return yarn_inverse_frequencies(self.rotary_dim, self.base, self.factor, self.original, self.fast, self.slow,
+                                        self.min_ramp_width)
+
+    def inverse_frequencies(self, device) -> torch.Tensor:
+        key = str(device)
+        t = self._inv_freq.get(key)
+        if t is None:
+            t = self._inv_freq[key] = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32).to(device)
+        return t
+
+
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
     pad_safe = True
@@ -106,3 +159,4 @@ class NoPositionEncoding(PositionEncoding):
 
 register_position_encoding("rope", RotaryPositionEncoding)
 register_position_encoding("none", NoPositionEncoding)
+register_position_encoding("yarn", YarnRotaryPositionEncoding)

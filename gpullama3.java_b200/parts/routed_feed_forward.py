@@ -5,6 +5,9 @@
     ``keep_groups`` best groups can be chosen; the ``top`` best of those are
     y = sum over the chosen e of  s_e / (sum of the chosen s + 1e-20) * down_e( act(gate_e h, up_e h) )
 
+With ``router="table"`` there is no router product: row ``token id`` of an integer table [vocabulary, top] names the token's
+experts, and every one of them weighs 1 / top.
+
 The router and the weights are 32-bit in both precisions.  The (token, choice) pairs are ordered by expert.  A step of
 few tokens then runs every expert's rows as a weight-streaming product whose row counts are read on the device, so a
 decode step's launches do not depend on the routing and can be recorded; an expert's weights are read once for all the
@@ -30,8 +33,13 @@ class RoutedFeedForward(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int, top: int, groups: int = 1,
                  keep_groups: int | None = None, activation: str = "silu", limit: float | None = None, slope: float = 1.0,
-                 weight_eps: float = 1e-20):
+                 weight_eps: float = 1e-20, router: str = "learned", vocab_size: int | None = None):
         keep_groups = groups if keep_groups is None else keep_groups
+        if router not in ("learned", "table"):
+            raise ConfigError(f"routed feed-forward: router {router!r}; known: learned, table")
+        if router == "table" and not vocab_size:
+            raise ConfigError("routed feed-forward: a routing table needs the vocabulary's size")
+        self.routing, self.vocab_size = router, int(vocab_size or 0)
         if activation not in ops.ACTIVATION_CODES:
             raise ConfigError(f"feed-forward activation {activation!r}; known: {', '.join(sorted(ops.ACTIVATION_CODES))}")
         if activation == "clamped_sigmoid" and (limit is None or not limit > 0):
@@ -49,7 +57,8 @@ class RoutedFeedForward(FeedForward):
         self.activation, self.gate_args, self.weight_eps = activation, (float(limit or 0.0), float(slope)), float(weight_eps)
 
     def parameters(self):
-        p = {"router": ParamSpec((self.n_experts, self.hidden_size))}
+        p = ({"router": ParamSpec((self.n_experts, self.hidden_size))} if self.routing == "learned" else
+             {"table": ParamSpec((self.vocab_size, self.top), "int_table", float(self.n_experts))})
         for e in range(self.n_experts):
             p[f"e{e}.gate"] = ParamSpec((self.intermediate_size, self.hidden_size))
             p[f"e{e}.up"] = ParamSpec((self.intermediate_size, self.hidden_size))
@@ -59,7 +68,10 @@ class RoutedFeedForward(FeedForward):
     def load(self, tensors, dtype, device):
         run = torch.float32 if dtype == torch.float32 else torch.bfloat16
         E, ff, h = self.n_experts, self.intermediate_size, self.hidden_size
-        self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+        if self.routing == "learned":
+            self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+        else:
+            self.table = tensors["table"].to(device=device, dtype=torch.int32).contiguous()
         self.w_gate_up = torch.empty((E, 2 * ff, h), dtype=run, device=device)   # gate and up rows interleaved
         self.w_down = torch.empty((E, h, ff), dtype=run, device=device)
         for e in range(E):
@@ -77,6 +89,9 @@ class RoutedFeedForward(FeedForward):
         T = x.shape[0]
         chosen = ctx.empty((T, self.top), torch.int32)
         weights = ctx.empty((T, self.top), torch.float32)
+        if self.routing == "table":
+            ops.moe_table_route(ctx.tokens, self.table, chosen, weights, self.n_experts)
+            return chosen, weights
         ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores)
         return chosen, weights
 

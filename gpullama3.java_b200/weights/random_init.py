@@ -74,7 +74,16 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_std: f
     made there by the kernel, with the bits the CPU would give."""
     device = torch.device(device)
     if spec.init == "int_table":
-        return torch.zeros(spec.shape, device=device, dtype=torch.int32)
+        # rows of distinct small integers: entry j of row r is (h(r) + j * odd(r)) mod 2^k, below ``spec.mean`` when that
+        # is given as the number of values (a power of two, or the row is reduced modulo it and may then repeat)
+        n_values = int(spec.mean) if spec.mean else 0
+        if not n_values or len(spec.shape) != 2:
+            return torch.zeros(spec.shape, device=device, dtype=torch.int32)
+        rows, cols = spec.shape
+        r = torch.arange(rows, dtype=torch.int64)
+        start = (r * 2654435761 + tensor_key(seed, name) % 1000003) % n_values
+        table = (start[:, None] + torch.arange(cols, dtype=torch.int64)[None, :]) % n_values
+        return table.to(torch.int32).to(device)
     if spec.init == "zeros" or (spec.init == "norm" and not norm_std):
         return torch.full(spec.shape, 0.0 if spec.init == "zeros" else 1.0, device=device, dtype=dtype)
     if any(d < 0 for d in spec.shape):
