@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--batch 8] [--context 4096] [--layers L] [--sizes all|none]
-    python bench.py --design guduzen|pekerax [--design-sizes s,m]     (another workload, see the end of this text)
+    python bench.py --design guduzen|pekerax|gatuzen [--design-sizes s,m]     (another workload, see the end of this text)
 
 Default run: the Llama-3.2-1B shape (BASELINE.json configs[2]) with random bfloat16 weights, a
 batch of 8 sequences at context length 4096.  A "step" is one decode step.  ``value`` is decoded
@@ -30,6 +30,12 @@ attention with kept first positions, distance penalty, sink, value mixing and ou
 the others routed: 8 experts of half the dense width, 2 per token) beside the Guduzen decoder, the closest existing
 model (window attention, delta rule, dense gated feed-forward), and the Llama 3 decoder, all of equal width, depth and
 heads.
+
+``--design gatuzen`` does the same for the Gatuzen decoder (layers in the order gated linear attention, state-space
+mixer, latent attention with a rotated shared key part and an output gate; every sublayer normed on both sides behind a
+4-tap input convolution; every feed-forward routed by a table from token id to experts: 8 experts of half the dense
+width, 2 per token) beside the Pekerax decoder, the closest existing model (delta rule on the same scan, routed
+feed-forward), and the Guduzen decoder (latent attention, delta rule), all of equal width, depth and heads.
 
 The library runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """
@@ -436,6 +442,24 @@ def pekerax_config(z):
             "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def gatuzen_config(z):
+    """Layers in the order gated linear attention, state-space mixer, latent attention (96 latent + 32 rotated dimensions:
+    one key/value head of 128), repeated; every sublayer normed on both sides and reading through a 4-tap convolution;
+    every feed-forward routed by table (8 experts of half the dense width, 2 per token: the same products per token as
+    the dense one)."""
+    H, d = z["heads"], z["dim"]
+    gla = {"heads": H, "dim": d, "vdim": d, "tau": 16.0, "decay_rank": 16}
+    ssd = {"heads": H, "vdim": d, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    lat = {"heads": H, "dim": d, "rot_dim": 32, "vdim": d, "kv_rank": z["kv_rank"] - 32, "scale": (d + 32) ** -0.5,
+           "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2}, "router": {"experts": 8, "top": 2}}
+    kinds = (("gla", gla), ("mamba2", ssd), ("latent_attention", lat))
+    layers = [{"type": kinds[i % 3][0], "mixer": dict(kinds[i % 3][1]), "mlp": moe} for i in range(z["layers"])]
+    return {"architecture": "Gatuzen", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "logit_scale": 1.0, "residual_mult": 1.0,
+            "layers": layers}
+
+
 def llama_like(z):
     return {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -513,6 +537,9 @@ DESIGNS = {
                 ("llama",)),
     "pekerax": (pekerax_config, "Pekerax, layers delta rule / attention / attention, first feed-forward dense, the others "
                                 "routed (8 experts, 2 per token)", ("guduzen", "llama")),
+    "gatuzen": (gatuzen_config, "Gatuzen, layers gated linear attention / state-space mixer / latent attention with a "
+                                "rotated shared key part, sublayers normed on both sides behind input convolutions, "
+                                "feed-forwards routed by table (8 experts, 2 per token)", ("pekerax", "guduzen")),
 }
 
 
@@ -524,7 +551,7 @@ def run_design(args, peaks, peak_source, clocks) -> int:
     sizes = {}
     name = args.design
     make, what, beside = DESIGNS[name]
-    others = {"guduzen": guduzen_config, "llama": llama_like}
+    others = {"guduzen": guduzen_config, "pekerax": pekerax_config, "llama": llama_like}
     for key in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES, reverse=True)):
         z = DESIGN_SIZES[key]
         sizes[key] = {"sizes": z, name: run_design_arm(make(z), f"{name} {key}", args, peaks)}

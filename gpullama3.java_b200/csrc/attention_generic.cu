@@ -23,6 +23,7 @@
 namespace b200 {
 
 constexpr int kAttnThreads = 128;
+constexpr int kMaxDimBlocks = 16;   // head sizes up to 512, 32 dimensions per block
 
 struct AttentionTerms {
     int keep_first;
@@ -91,15 +92,15 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
     const float slope = terms.slopes ? terms.slopes[h] : 0.f;
     const size_t page_stride = (size_t)n_kv_heads * kPageTokens * head_dim;
     const size_t head_off = (size_t)g * kPageTokens * head_dim;
-    const int dim_blocks = (head_dim + 31) / 32;     // at most 8
+    const int dim_blocks = (head_dim + 31) / 32;     // at most kMaxDimBlocks
 
     const T* qr = q + (size_t)t * q_row_stride + (size_t)h * head_dim;
     for (int d = tid; d < head_dim; d += kAttnThreads) q_s[d] = to_f32<T>(qr[d]);
     __syncthreads();
 
-    float acc[8];                            // lane l: dimensions 32 b + l of this warp's keys
+    float acc[kMaxDimBlocks];                // lane l: dimensions 32 b + l of this warp's keys
 #pragma unroll
-    for (int b = 0; b < 8; ++b) acc[b] = 0.f;
+    for (int b = 0; b < kMaxDimBlocks; ++b) acc[b] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     if (terms.sinks && split == 0) {
         m_run = terms.sinks[h];
@@ -147,7 +148,7 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
         const T* vr = nullptr;
         if (key <= last) vr = v_pool + (size_t)pages[j / kPageTokens] * page_stride + head_off + (j % kPageTokens);
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
+        for (int b = 0; b < kMaxDimBlocks; ++b) {
             if (b >= dim_blocks) break;
             acc[b] *= corr;
             if (!any) continue;
@@ -174,7 +175,7 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
 
     // the four warps' partial outputs meet in shared memory and are added in warp order
 #pragma unroll
-    for (int b = 0; b < 8; ++b)
+    for (int b = 0; b < kMaxDimBlocks; ++b)
         if (b < dim_blocks) part[(warp * dim_blocks + b) * 32 + lane] = acc[b];
     __syncthreads();
     T* o = out + ((size_t)t * n_heads + h) * head_dim;
@@ -227,7 +228,7 @@ extern "C" int b200_attention_paged(const void* q, int q_row_stride, void* out, 
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) return b200::kErrBadArgument;
     const b200::AttentionTerms terms = {keep_first, slopes, sinks, gate, ld_gate};
     if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && scratch == nullptr)) return b200::kErrBadArgument;
-    if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256) return b200::kErrUnsupportedSize;
+    if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 32 * b200::kMaxDimBlocks) return b200::kErrUnsupportedSize;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return b200::kErrBadArgument;
     const size_t smem = sizeof(float) * (head_dim + b200::kAttnThreads + 33 + (size_t)(b200::kAttnThreads / 32) * ((head_dim + 31) / 32) * 32);
     dim3 grid(n_tokens, n_heads, n_splits);

@@ -13,7 +13,7 @@ from .build import KernelBuildError, library
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64  # must equal b200::kPageTokens
 # what the plain kernels, which take every size the others refuse, are built for
-HEAD_DIM_STEP, MAX_HEAD_DIM = 16, 256   # attention_generic.cu
+HEAD_DIM_STEP, MAX_HEAD_DIM = 16, 512   # attention_generic.cu
 MAX_ROTARY_DIM = 512                    # rope_cache.cu
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}

@@ -97,7 +97,9 @@ def mamba2(h, W, p, m, norm_eps):
 # ---------------------------------------------------------------- latent attention
 def yarn_frequencies(rot):
     """Per pair i: the rotation frequency, and the factor on cosine and sine."""
-    dims, base, s = rot["dims"], float(rot["base"]), rot["scaling"]
+    dims, base, s = rot["dims"], float(rot["base"]), rot.get("scaling")
+    if not s:       # no stretching: the plain frequencies, and nothing on cosine and sine
+        return torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=F), 1.0
     factor, original = float(s["factor"]), float(s["original"])
 
     def dim_of(turns):
@@ -175,22 +177,26 @@ def layer_runs(config):
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(config, weights, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and, asked for, the residual stream after every layer run)."""
+def forward(config, weights, tokens, return_layers=False, reads=None):
+    """Logits [T, vocab] of one whole sequence (and, asked for, the residual stream after every layer run).
+    ``reads``, if given, is applied to what every sublayer reads (to see how far a small change there moves the logits)."""
     W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, groups, mult = float(config["norm"]["eps"]), config["norm"]["groups"], float(config["residual_mult"])
     tokens = torch.as_tensor(tokens, dtype=torch.int64)
+    taps = (config.get("canon") or {}).get("taps", 0)
+    convolved = (lambda h, w: with_input_convolution(h, W[w])) if taps else (lambda h, w: h)
+    read = convolved if reads is None else (lambda h, w: reads(convolved(h, w)))
     x = W["embed"][tokens] * float(config["embedding"]["scale"])
     after = []
     for i, enters in layer_runs(config):
         L, p = config["layers"][i], f"l{i}."
         if enters is not None:
             x = x + W["loop.step"][enters]
-        h = with_input_convolution(grouped_rms_norm(x, W[p + "norm1"], groups, eps), W[p + "canon1"])
+        h = read(grouped_rms_norm(x, W[p + "norm1"], groups, eps), p + "canon1")
         y = MIXERS[L["type"]](h, W, p + "mix.", L["mixer"], eps)
         x = x + mult * grouped_rms_norm(y, W[p + "norm1b"], groups, eps)
         if L.get("mlp") is not None:
-            h = with_input_convolution(grouped_rms_norm(x, W[p + "norm2"], groups, eps), W[p + "canon2"])
+            h = read(grouped_rms_norm(x, W[p + "norm2"], groups, eps), p + "canon2")
             y = table_mixture_of_experts(h, tokens, W, p + "mlp.", L["mlp"]["router"]["top"])
             x = x + mult * grouped_rms_norm(y, W[p + "norm2b"], groups, eps)
         after.append(x)

@@ -12,7 +12,7 @@ import torch
 
 import plain_gatuzen
 from conftest import ROOT, random_prompts
-from gatuzen_helpers import CONFIGS, assert_logits, make_gatuzen_dir, plain_inputs
+from gatuzen_helpers import CONFIGS, assert_logits, make_gatuzen_dir, plain_inputs, reference
 from replay_helpers import (max_live_tokens, read_rows, run_in_process, trace_batches, trace_tail_one_by_one,
                             trace_whole, write_trace)
 
@@ -28,7 +28,7 @@ def setup(request, session_tmp):
     cfg, weights = plain_inputs(d)
     prompts = random_prompts(cfg["vocab"], LENGTHS, seed=17)
     requests = {f"r{i}": p for i, p in enumerate(prompts)}
-    refs = {rid: plain_gatuzen.forward(cfg, weights, toks) for rid, toks in requests.items()}
+    refs = {rid: reference(cfg, weights, toks) for rid, toks in requests.items()}
     return d, cfg, weights, requests, refs
 
 
