@@ -159,6 +159,98 @@ __global__ void causal_conv_kernel(const TI* __restrict__ x, int ld_x, const flo
     }
 }
 
+// The same convolution for steps of many tokens: a thread takes 4 neighbouring channels of kConvRun consecutive tokens of
+// the step.  It asks for all the rows it needs at once (the run's own and the MAXT - 1 before it: 16 or 8 bytes per
+// row), so every input row is fetched from memory once per run instead of once per tap, and then walks the run; a token
+// among the first taps - 1 of its sequence takes its older inputs from the slot's state.  Sums run from the oldest tap
+// to the newest, as in the kernel above.
+constexpr int kConvRun = 8;
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&f)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&f)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename TI, typename TO, int MAXT>
+__global__ void __launch_bounds__(128)
+causal_conv_run_kernel(const TI* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ bias,
+                       const float* __restrict__ state, size_t slot_stride, const int* __restrict__ slots,
+                       const int* __restrict__ seq_ids, const int* __restrict__ cu_seqlens, TO* __restrict__ out, int ld_out,
+                       int channels, int taps, int activation, int add_input, int n_tokens) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= channels) return;
+    const int t0 = blockIdx.y * kConvRun;
+    // rows t0 - (MAXT - 1) .. t0 + kConvRun - 1 of the step (those of them that exist and that some tap reads)
+    float rows[kConvRun + MAXT - 1][4];
+    int seq[kConvRun], first[kConvRun];
+#pragma unroll
+    for (int k = 0; k < kConvRun + MAXT - 1; ++k) {
+        const int t = t0 - (MAXT - 1) + k;
+        if (t >= 0 && t < n_tokens && (MAXT - 1 - k) <= taps - 1) {
+            load4<TI>(x + (size_t)t * ld_x + c, rows[k]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) rows[k][e] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kConvRun; ++i) seq[i] = t0 + i < n_tokens ? seq_ids[t0 + i] : 0;
+#pragma unroll
+    for (int i = 0; i < kConvRun; ++i) first[i] = cu_seqlens[seq[i]];
+    // tap j of the layer stands at wt[MAXT - taps + j]: the newest tap last, zeros in front of the oldest
+    float wt[MAXT][4], b[4];
+#pragma unroll
+    for (int m = 0; m < MAXT; ++m) {
+        const int j = m - (MAXT - taps);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wt[m][e] = j >= 0 ? w[(size_t)(c + e) * taps + j] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) b[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kConvRun; ++i) {
+        const int t = t0 + i;
+        if (t >= n_tokens) break;
+        const int local = t - first[i];
+        float acc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = b[e];
+#pragma unroll
+        for (int m = 0; m < MAXT; ++m) {
+            const int back = MAXT - 1 - m;
+            if (back > taps - 1) continue;
+            if (local - back >= 0) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] += wt[m][e] * rows[i + m][e];
+            } else {
+                const float* st = state + (size_t)slots[seq[i]] * slot_stride + (size_t)(taps - 1 + local - back) * channels + c;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] += wt[m][e] * st[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (activation == 1) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+            if (add_input) acc[e] += rows[i + MAXT - 1][e];
+        }
+        store4<TO>(out + (size_t)t * ld_out + c, acc);
+    }
+}
+
 // What the scan needs of every token, made by a kernel of its own over all tokens at once (a warp per token and head):
 // one row of 32-bit numbers per (head, token), [q | k | g (each d_pad wide, zeros behind the d_k) | v (d_v) | beta | k . q | skip (unused here) | fill
 // to a multiple of 4], q and k of unit length (q also scaled), g = exp(-exp(A_log) softplus(a + dt_bias)),
@@ -438,14 +530,27 @@ extern "C" int b200_causal_conv_silu(const void* x, int ld_x, const float* w, fl
     const int vec = dtype == b200::kF32 ? 4 : 8;
     const bool wide = channels % vec == 0 && ld_x % vec == 0 && ld_out % vec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
     const dim3 grid_v((channels / vec + 127) / 128, n_tokens);
-    if (dtype == b200::kF32 && wide)
+    // steps of many tokens: runs of tokens per thread (the general kernel with SiLU, no bias, nothing added)
+    const bool runs = wide && n_tokens >= 8 * b200::kConvRun && taps <= 8;
+    const dim3 grid_r((channels / 4 + 127) / 128, (n_tokens + b200::kConvRun - 1) / b200::kConvRun);
+    if (runs) {
+        B200_DISPATCH_DTYPE(dtype, T,
+            if (taps <= 4)
+                b200::causal_conv_run_kernel<T, T, 4><<<grid_r, 128, 0, stream>>>((const T*)x, ld_x, w, nullptr, state, (size_t)slot_stride,
+                                                                                slots, seq_ids, cu_seqlens, (T*)out, ld_out, channels,
+                                                                                taps, 1, 0, n_tokens);
+            else
+                b200::causal_conv_run_kernel<T, T, 8><<<grid_r, 128, 0, stream>>>((const T*)x, ld_x, w, nullptr, state, (size_t)slot_stride,
+                                                                                slots, seq_ids, cu_seqlens, (T*)out, ld_out, channels,
+                                                                                taps, 1, 0, n_tokens));
+    } else if (dtype == b200::kF32 && wide)
         b200::causal_conv_silu_kernel<float, 4><<<grid_v, 128, 0, stream>>>((const float*)x, ld_x, w, state, (size_t)slot_stride, slots,
                                                                             seq_ids, cu_seqlens, (float*)out, ld_out, channels, taps);
     else if (dtype == b200::kBF16 && wide)
         b200::causal_conv_silu_kernel<__nv_bfloat16, 8><<<grid_v, 128, 0, stream>>>((const __nv_bfloat16*)x, ld_x, w, state, (size_t)slot_stride, slots,
                                                                                     seq_ids, cu_seqlens, (__nv_bfloat16*)out, ld_out, channels, taps);
     B200_DISPATCH_DTYPE(dtype, T,
-        if (!wide)
+        if (!wide && !runs)
             b200::causal_conv_silu_kernel<T, 1><<<grid, 128, 0, stream>>>((const T*)x, ld_x, w, state, (size_t)slot_stride, slots,
                                                                           seq_ids, cu_seqlens, (T*)out, ld_out, channels, taps);
         if (update_state && taps > 1)
@@ -465,9 +570,22 @@ extern "C" int b200_causal_conv(const void* x, int ld_x, int in_dtype, const flo
     if (n_tokens > 65535 || n_seqs > 65535) return b200::kErrUnsupportedSize;
     const bool wide = channels % 4 == 0;
     const dim3 grid(((wide ? channels / 4 : channels) + 127) / 128, n_tokens), grid_u((channels + 127) / 128, n_seqs);
+    // steps of many tokens, when every access of four channels is aligned: runs of tokens per thread
+    const size_t in_size = in_dtype == b200::kF32 ? 4 : 2, out_size = out_dtype == b200::kF32 ? 4 : 2;
+    const bool runs = wide && n_tokens >= 8 * b200::kConvRun && taps <= 8 && ld_x % 4 == 0 && ld_out % 4 == 0 &&
+                      (uintptr_t)x % (4 * in_size) == 0 && (uintptr_t)out % (4 * out_size) == 0;
+    const dim3 grid_r((channels / 4 + 127) / 128, (n_tokens + b200::kConvRun - 1) / b200::kConvRun);
     B200_DISPATCH_DTYPE(in_dtype, TI,
         B200_DISPATCH_DTYPE2(out_dtype, TO,
-            if (wide)
+            if (runs && taps <= 4)
+                b200::causal_conv_run_kernel<TI, TO, 4><<<grid_r, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                                  slots, seq_ids, cu_seqlens, (TO*)out, ld_out, channels,
+                                                                                  taps, activation, add_input, n_tokens);
+            else if (runs)
+                b200::causal_conv_run_kernel<TI, TO, 8><<<grid_r, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                                  slots, seq_ids, cu_seqlens, (TO*)out, ld_out, channels,
+                                                                                  taps, activation, add_input, n_tokens);
+            else if (wide)
                 b200::causal_conv_kernel<TI, TO, 4><<<grid, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
                                                                             slots, seq_ids, cu_seqlens, (TO*)out, ld_out, channels,
                                                                             taps, activation, add_input);

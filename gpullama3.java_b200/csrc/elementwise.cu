@@ -4,7 +4,8 @@
 //                      per (token, head) row of 32-bit numbers: the output norm of a recurrent mixer; with `gate_first`
 //                      the row is multiplied by act(gate) first and the norm runs over the gated row; with
 //                      `weight_per_row` every row has weights of its own (w holds n_heads * d numbers), so that the rows
-//                      may be any equal parts of the mixer's output, not its heads
+//                      may be any equal parts of the mixer's output, not its heads; a warp per row, or a CTA per row
+//                      of 512 numbers and more
 //   gate_rows          x[t, :n] <- x[t, :n] * sigmoid(gate[t, :n]) (or SiLU), in place: a gate on a mixer's output
 //   scale_rows         x <- x * s, in place on 32-bit logits
 #include "common.cuh"
@@ -45,6 +46,47 @@ gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, c
         o[e] = from_f32<T>(gate_first ? (xr[e] * act(e)) * scale * wr[e] : xr[e] * scale * wr[e] * act(e));
 }
 
+// a CTA per row, for rows too long for one warp (a norm over a large part of the mixer's output); the gated values stay
+// in registers between the two passes when the row has at most kWideKeep numbers per thread
+constexpr int kWideThreads = 256, kWideKeep = 8;
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads)
+gated_rmsnorm_wide_kernel(const float* __restrict__ x, const float* __restrict__ w, const T* __restrict__ gate, int ld_gate,
+                          T* __restrict__ out, int n_heads, int d, float eps, int gate_act, int gate_first, int weight_per_row) {
+    __shared__ float scratch[33];
+    const int row = blockIdx.x;
+    const int t = row / n_heads, h = row % n_heads;
+    const float* xr = x + (size_t)row * d;
+    const T* g = gate + (size_t)t * ld_gate + (size_t)h * d;
+    const float* wr = w + (weight_per_row ? (size_t)h * d : 0);
+    auto act = [&](int e) {
+        const float z = to_f32<T>(g[e]);
+        const float sig = 1.0f / (1.0f + expf(-z));
+        return gate_act == 1 ? z * sig : sig;
+    };
+    float keep[kWideKeep], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWideKeep; ++i) {
+        const int e = threadIdx.x + i * kWideThreads;
+        keep[i] = e < d ? (gate_first ? xr[e] * act(e) : xr[e]) : 0.f;
+        ss += keep[i] * keep[i];
+    }
+    for (int e = threadIdx.x + kWideKeep * kWideThreads; e < d; e += kWideThreads) {
+        const float v = gate_first ? xr[e] * act(e) : xr[e];
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    T* o = out + (size_t)row * d;
+#pragma unroll
+    for (int i = 0; i < kWideKeep; ++i) {
+        const int e = threadIdx.x + i * kWideThreads;
+        if (e < d) o[e] = from_f32<T>(gate_first ? keep[i] * scale * wr[e] : keep[i] * scale * wr[e] * act(e));
+    }
+    for (int e = threadIdx.x + kWideKeep * kWideThreads; e < d; e += kWideThreads)
+        o[e] = from_f32<T>(gate_first ? (xr[e] * act(e)) * scale * wr[e] : xr[e] * scale * wr[e] * act(e));
+}
+
 template <typename T>
 __global__ void gate_rows_kernel(T* __restrict__ x, int ld_x, const T* __restrict__ gate, int ld_gate, int n, int gate_act) {
     T* xr = x + (size_t)blockIdx.x * ld_x;
@@ -77,10 +119,16 @@ extern "C" int b200_gated_rmsnorm(const float* x, const float* w, const void* ga
     if (n_tokens <= 0 || n_heads <= 0) return 0;
     if (d < 1) return b200::kErrBadArgument;
     const long long rows = (long long)n_tokens * n_heads;
+    if (rows > 0x7fffffffLL) return b200::kErrUnsupportedSize;
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::gated_rmsnorm_kernel<T><<<(int)((rows + 3) / 4), 128, 0, stream>>>(x, w, (const T*)gate, ld_gate, (T*)out,
-                                                                                 n_heads, d, (int)rows, eps, gate_act, gate_first,
-                                                                                 weight_per_row));
+        if (d >= 512)      // (a warp would walk such a row in 16 or more rounds, twice)
+            b200::gated_rmsnorm_wide_kernel<T><<<(int)rows, b200::kWideThreads, 0, stream>>>(x, w, (const T*)gate, ld_gate, (T*)out,
+                                                                                           n_heads, d, eps, gate_act, gate_first,
+                                                                                           weight_per_row);
+        else
+            b200::gated_rmsnorm_kernel<T><<<(int)((rows + 3) / 4), 128, 0, stream>>>(x, w, (const T*)gate, ld_gate, (T*)out,
+                                                                                     n_heads, d, (int)rows, eps, gate_act, gate_first,
+                                                                                     weight_per_row));
     return b200::launch_status();
 }
 

@@ -96,6 +96,51 @@ def test_convolution_carries_its_inputs(dtype, taps, channels, bias, act, add):
 
 
 @DTYPES
+@pytest.mark.parametrize("taps, channels", [(4, 64), (2, 520), (7, 36), (1, 8), (9, 12), (4, 30)])
+@pytest.mark.parametrize("form", ["added", "bias and silu", "silu alone"])
+def test_convolution_over_long_steps(dtype, taps, channels, form):
+    """Steps of 154 and 200 tokens (threads then take runs of tokens): four sequences whose borders fall inside a run,
+    one of a single token, the second step reading what the first left in the slots; input rows wider than the
+    channels.  32-bit inputs with a rounded result as well as equal types."""
+    from gpullama3.java_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(taps * channels + len(form))
+    lens = [150, 3, 200, 1]
+    xs = [torch.randn(n, channels, generator=g).to(dtype).float() for n in lens]
+    w = torch.randn(channels, taps, generator=g)
+    b = torch.randn(channels, generator=g) if form == "bias and silu" else None
+    refs = []
+    for x in xs:
+        r = P.causal_conv(x.to(F), w.to(F), b.to(F) if b is not None else None)
+        refs.append(r + x.to(F) if form == "added" else P.silu(r))
+    in_dtype = torch.float32 if form == "added" else dtype
+    state = torch.zeros(6, max(taps - 1, 1) * channels + 4, device="cuda")
+    slots = [5, 1, 0, 3]
+    got, at = [[] for _ in lens], [0] * 4
+    for portions in ([61, 2, 90, 1], [89, 1, 110, 0]):
+        live = [i for i, n in enumerate(portions) if n]
+        x = torch.zeros(sum(portions), channels + 8, dtype=in_dtype, device="cuda")
+        x[:, :channels] = torch.cat([xs[i][at[i]:at[i] + portions[i]] for i in live]).to(in_dtype)
+        cu = torch.tensor([0] + list(torch.tensor([portions[i] for i in live]).cumsum(0)), dtype=torch.int32).cuda()
+        seq = torch.cat([torch.full((portions[i],), j, dtype=torch.int32) for j, i in enumerate(live)]).cuda()
+        out = torch.empty((sum(portions), channels), dtype=dtype, device="cuda")
+        slot_ids = torch.tensor([slots[i] for i in live], dtype=torch.int32).cuda()
+        if form == "silu alone":
+            ops.causal_conv_silu(x, w.cuda(), state, slot_ids, seq, cu, out, channels)
+        else:
+            ops.causal_conv(x, w.cuda(), state, slot_ids, seq, cu, out, channels, bias=b.cuda() if b is not None else None,
+                            activation=None if form == "added" else "silu", add_input=form == "added")
+        o = 0
+        for i in live:
+            got[i].append(out[o:o + portions[i]].float().cpu())
+            o += portions[i]
+            at[i] += portions[i]
+    for i in range(4):
+        _close(torch.cat(got[i]), refs[i], dtype, f"sequence {i}", f32=1e-5, bf16=2e-2)
+    assert float(state[2].abs().max()) == 0.0 and float(state[4].abs().max()) == 0.0    # slots no sequence holds
+
+
+@DTYPES
 @pytest.mark.parametrize("heads, kv_heads, dk, dv", [(2, 2, 48, 64), (4, 2, 24, 16), (1, 1, 130, 8), (3, 1, 8, 40)])
 @pytest.mark.parametrize("kind", ["gated linear attention", "state space"])
 def test_scan_without_correction(dtype, heads, kv_heads, dk, dv, kind):
@@ -155,7 +200,7 @@ def test_scan_without_correction(dtype, heads, kv_heads, dk, dv, kind):
 
 
 @DTYPES
-@pytest.mark.parametrize("rows, parts, d", [(5, 4, 16), (3, 1, 200), (9, 3, 40)])
+@pytest.mark.parametrize("rows, parts, d", [(5, 4, 16), (3, 1, 200), (9, 3, 40), (3, 2, 520), (2, 1, 2304)])
 def test_gate_before_the_output_norm(dtype, rows, parts, d):
     from gpullama3.java_b200.kernels import ops
 
