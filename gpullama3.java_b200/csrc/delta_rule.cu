@@ -17,7 +17,8 @@
 //
 // The convolution: channel c of token t gets sum_j w[c, j] x[t - (taps - 1) + j, c] followed by SiLU, where inputs
 // before the step's first token come from the slot's state (the last taps - 1 inputs of the sequence, zero at its
-// start); conv_state_update then stores the step's last taps - 1 inputs there.
+// start); conv_state_update then stores the step's last taps - 1 inputs there (a step in which every sequence brings
+// one token does both in one kernel, causal_conv_single).
 //
 // The same scan also runs the recurrences without the delta correction (linear_scan): S <- diag(g) S + k (beta v)^T,
 // o = S^T q + skip v, which is gated linear attention (a decay per key channel, g = sigmoid(.)^(1/tau), beta = 1) and the
@@ -248,6 +249,68 @@ causal_conv_run_kernel(const TI* __restrict__ x, int ld_x, const float* __restri
             if (add_input) acc[e] += rows[i + MAXT - 1][e];
         }
         store4<TO>(out + (size_t)t * ld_out + c, acc);
+    }
+}
+
+// The same convolution for steps in which every sequence brings exactly one token (decoding): the token's older inputs
+// all come from its slot's state, and the thread that read them also moves the state on by one token, so the step needs
+// no second kernel.  VEC neighbouring channels per thread; sums run from the oldest tap to the newest as above.
+template <typename TI, typename TO, int VEC>
+__global__ void __launch_bounds__(128)
+causal_conv_single_kernel(const TI* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ bias,
+                          float* __restrict__ state, size_t slot_stride, const int* __restrict__ slots,
+                          const int* __restrict__ seq_ids, TO* __restrict__ out, int ld_out, int channels, int taps,
+                          int activation, int add_input, int update_state) {
+    const int t = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c >= channels) return;
+    float* st = state + (size_t)slots[seq_ids[t]] * slot_stride + c;   // [taps - 1][channels], oldest first
+    float own[VEC], acc[VEC], newer[VEC];
+    if constexpr (VEC == 4) {
+        load4<TI>(x + (size_t)t * ld_x + c, own);
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) own[e] = to_f32<TI>(x[(size_t)t * ld_x + c + e]);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int m = 0; m + 1 < taps; ++m) {
+        if constexpr (VEC == 4) {
+            load4<float>(st + (size_t)m * channels, newer);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) newer[e] = st[(size_t)m * channels + e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += w[(size_t)(c + e) * taps + m] * newer[e];
+        if (update_state && m > 0) {
+            if constexpr (VEC == 4) {
+                store4<float>(st + (size_t)(m - 1) * channels, newer);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) st[(size_t)(m - 1) * channels + e] = newer[e];
+            }
+        }
+    }
+    if (update_state && taps > 1) {
+        if constexpr (VEC == 4) {
+            store4<float>(st + (size_t)(taps - 2) * channels, own);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) st[(size_t)(taps - 2) * channels + e] = own[e];
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        acc[e] += w[(size_t)(c + e) * taps + taps - 1] * own[e];
+        if (activation == 1) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+        if (add_input) acc[e] += own[e];
+    }
+    if constexpr (VEC == 4) {
+        store4<TO>(out + (size_t)t * ld_out + c, acc);
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) out[(size_t)t * ld_out + c + e] = from_f32<TO>(acc[e]);
     }
 }
 
@@ -533,6 +596,23 @@ extern "C" int b200_causal_conv_silu(const void* x, int ld_x, const float* w, fl
     // steps of many tokens: runs of tokens per thread (the general kernel with SiLU, no bias, nothing added)
     const bool runs = wide && n_tokens >= 8 * b200::kConvRun && taps <= 8;
     const dim3 grid_r((channels / 4 + 127) / 128, (n_tokens + b200::kConvRun - 1) / b200::kConvRun);
+    // every sequence brings one token: one kernel reads the slot's state and moves it on
+    if (n_tokens == n_seqs) {
+        const size_t size = dtype == b200::kF32 ? 4 : 2;
+        const bool wide4 = channels % 4 == 0 && ld_x % 4 == 0 && ld_out % 4 == 0 && slot_stride % 4 == 0 &&
+                           (uintptr_t)x % (4 * size) == 0 && (uintptr_t)out % (4 * size) == 0 && (uintptr_t)state % 16 == 0;
+        const dim3 grid_s(((wide4 ? channels / 4 : channels) + 127) / 128, n_tokens);
+        B200_DISPATCH_DTYPE(dtype, T,
+            if (wide4)
+                b200::causal_conv_single_kernel<T, T, 4><<<grid_s, 128, 0, stream>>>((const T*)x, ld_x, w, nullptr, state, (size_t)slot_stride,
+                                                                                   slots, seq_ids, (T*)out, ld_out, channels, taps, 1, 0,
+                                                                                   update_state);
+            else
+                b200::causal_conv_single_kernel<T, T, 1><<<grid_s, 128, 0, stream>>>((const T*)x, ld_x, w, nullptr, state, (size_t)slot_stride,
+                                                                                   slots, seq_ids, (T*)out, ld_out, channels, taps, 1, 0,
+                                                                                   update_state));
+        return b200::launch_status();
+    }
     if (runs) {
         B200_DISPATCH_DTYPE(dtype, T,
             if (taps <= 4)
@@ -575,6 +655,23 @@ extern "C" int b200_causal_conv(const void* x, int ld_x, int in_dtype, const flo
     const bool runs = wide && n_tokens >= 8 * b200::kConvRun && taps <= 8 && ld_x % 4 == 0 && ld_out % 4 == 0 &&
                       (uintptr_t)x % (4 * in_size) == 0 && (uintptr_t)out % (4 * out_size) == 0;
     const dim3 grid_r((channels / 4 + 127) / 128, (n_tokens + b200::kConvRun - 1) / b200::kConvRun);
+    // every sequence brings one token: one kernel reads the slot's state and moves it on
+    if (n_tokens == n_seqs) {
+        const bool wide4 = wide && ld_x % 4 == 0 && ld_out % 4 == 0 && slot_stride % 4 == 0 && (uintptr_t)x % (4 * in_size) == 0 &&
+                           (uintptr_t)out % (4 * out_size) == 0 && (uintptr_t)state % 16 == 0;
+        const dim3 grid_s(((wide4 ? channels / 4 : channels) + 127) / 128, n_tokens);
+        B200_DISPATCH_DTYPE(in_dtype, TI,
+            B200_DISPATCH_DTYPE2(out_dtype, TO,
+                if (wide4)
+                    b200::causal_conv_single_kernel<TI, TO, 4><<<grid_s, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                                         slots, seq_ids, (TO*)out, ld_out, channels, taps,
+                                                                                         activation, add_input, update_state);
+                else
+                    b200::causal_conv_single_kernel<TI, TO, 1><<<grid_s, 128, 0, stream>>>((const TI*)x, ld_x, w, bias, state, (size_t)slot_stride,
+                                                                                         slots, seq_ids, (TO*)out, ld_out, channels, taps,
+                                                                                         activation, add_input, update_state)));
+        return b200::launch_status();
+    }
     B200_DISPATCH_DTYPE(in_dtype, TI,
         B200_DISPATCH_DTYPE2(out_dtype, TO,
             if (runs && taps <= 4)

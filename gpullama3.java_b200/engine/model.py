@@ -180,6 +180,12 @@ class CausalLM:
                     # the next run's offset joins the stream before that run's norm: a block that can add it in its own
                     # last kernel is handed the row, any other block leaves the norm to the next one
                     then = block.with_offset(then, self.pass_offsets.row(self.schedule[k + 1].enters))
+                if then is not None:
+                    # what the next block does to its first normed rows, if the block before it may do that too
+                    ahead = self.schedule[k + 1]
+                    read = nxt.first_read(ctx, cache.view(ahead.cache) if ahead.cache is not None else None, ahead.writes_cache)
+                    if read is not None:
+                        then = block.with_read(then, read)
                 handed = block.forward(residual, ctx, view, entry.writes_cache, x_in=handed, then_norm=then)
             else:
                 block.forward(residual, ctx, view, entry.writes_cache)

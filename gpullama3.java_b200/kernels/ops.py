@@ -93,6 +93,9 @@ _SIGNATURES = {
     "b200_group_rmsnorm": ("sandwich", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float]),
     "b200_sandwich_step": ("sandwich", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_float]),
+    "b200_sandwich_step_conv": ("sandwich", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_int, c_int, c_float, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int,
+                                             c_int]),
     "b200_add_row": ("sandwich", [c_void_p, c_void_p, c_int, c_int]),
     "b200_causal_conv": ("delta_rule", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -974,6 +977,36 @@ def sandwich_step(y: torch.Tensor, weight: torch.Tensor, mult: float, x: torch.T
     _check(_fn("b200_sandwich_step")(y.data_ptr(), weight.data_ptr(), float(mult), x.data_ptr(), ptr(offset), ptr(next_weight),
                                      ptr(out), dtype_code(out.dtype) if out is not None else F32, x.shape[0], x.shape[1],
                                      int(groups), float(eps), _stream()), "sandwich_step")
+
+
+def sandwich_step_conv_fits(dim: int, groups: int) -> bool:
+    """Whether ``sandwich_step_conv`` takes rows of ``dim`` numbers normed in ``groups`` parts (whole pieces of 128
+    numbers per part, at most 8192 numbers: the sizes of sandwich_step_rows_kernel in sandwich.cu)."""
+    return groups >= 1 and dim % groups == 0 and (dim // groups) % 128 == 0 and dim <= 8192
+
+
+def sandwich_step_conv(y: torch.Tensor, weight: torch.Tensor, mult: float, x: torch.Tensor, eps: float, groups: int,
+                       next_weight: torch.Tensor, out: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor,
+                       slots: torch.Tensor, *, offset: torch.Tensor | None = None, update_state: bool = True) -> None:
+    """``sandwich_step`` for a step in which every sequence brings one token, with the convolution over time that the
+    next reader applies to the normed rows h: out = h + sum_j conv_weight[:, j] h_(t - taps + 1 + j).  The older inputs
+    are rows of ``conv_state`` [slots, >= (taps - 1) * dim] (oldest first) at ``slots[t]``; with ``update_state`` the
+    state moves on by this token.  ``out`` may be of the run's type."""
+    _dev(y, weight, x, offset, next_weight, out, conv_weight, conv_state, slots)
+    T, dim = x.shape
+    taps = conv_weight.shape[1]
+    assert x.dtype == y.dtype == weight.dtype == next_weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+    assert x.shape == y.shape == out.shape and out.is_contiguous() and weight.numel() == dim and next_weight.numel() == dim
+    assert weight.is_contiguous() and next_weight.is_contiguous()
+    assert offset is None or (offset.dtype == torch.float32 and offset.is_contiguous() and offset.numel() == dim)
+    assert conv_weight.dtype == conv_state.dtype == torch.float32 and conv_weight.is_contiguous() and conv_weight.shape[0] == dim
+    assert conv_state.stride(1) == 1 and (taps < 2 or conv_state.shape[1] >= (taps - 1) * dim)
+    assert slots.dtype == torch.int32 and slots.numel() == T
+    _check(_fn("b200_sandwich_step_conv")(y.data_ptr(), weight.data_ptr(), float(mult), x.data_ptr(),
+                                          offset.data_ptr() if offset is not None else None, next_weight.data_ptr(),
+                                          out.data_ptr(), dtype_code(out.dtype), T, dim, int(groups), float(eps),
+                                          conv_weight.data_ptr(), conv_state.data_ptr(), conv_state.stride(0), slots.data_ptr(),
+                                          taps, int(bool(update_state)), _stream()), "sandwich_step_conv")
 
 
 def add_row(x: torch.Tensor, row: torch.Tensor) -> None:

@@ -203,6 +203,33 @@ class Block(Part):
         norms, or None when it cannot (the model then adds the row and the next block norms for itself)."""
         return None
 
+    def first_read(self, ctx: StepContext, cache, writes_cache: bool):
+        """What the block does to the rows of its first norm before its mixer reads them (a ``FirstRead``), offered
+        to the block that runs before it so that its last kernel can do that too; None when there is nothing to
+        offer in this step.  ``cache`` and ``writes_cache`` are what the block's own ``forward`` will be given."""
+        return None
+
+    def with_read(self, then_norm, read):
+        """``then_norm`` (as ``with_offset`` left it) when the next block offers ``read``: what this block wants as
+        ``then_norm`` so that it hands over rows that are read already (a ``ReadRows``); unchanged when it cannot."""
+        return then_norm
+
+
+@dataclass
+class FirstRead:
+    """A convolution over time on a block's first normed rows in a step in which every sequence brings one token:
+    out = h + sum_j weight[:, j] h_(t - taps + 1 + j) with the older inputs in ``state[slot]`` (oldest first), which moves on
+    by the token when ``writes``."""
+    weight: torch.Tensor     # float32 [dim, taps]
+    state: torch.Tensor      # float32 [max_slots, >= (taps - 1) * dim]
+    writes: bool
+
+
+@dataclass
+class ReadRows:
+    """Rows handed to the next block that are normed and read already (its ``FirstRead`` applied, in the run's type)."""
+    data: torch.Tensor
+
 
 def all_parts(root: Part, prefix: str = "") -> dict[str, Part]:
     """Every part below ``root`` by dotted path (``mixer``, ``mixer.position``), parents before children."""

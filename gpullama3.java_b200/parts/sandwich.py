@@ -21,14 +21,15 @@ from ..cache.sequence_cache import EntryNeeds, StateNeed
 from ..config.base import ConfigError
 from ..kernels import ops
 from ..weights.loader import ParamSpec
-from .base import Block, StepContext, all_parts, register_block
+from .base import Block, FirstRead, ReadRows, StepContext, all_parts, register_block
 
 
 class NormThenOffset:
-    """What a block is handed as ``then_norm`` when a vector joins the stream between it and the next block."""
+    """What a block is handed as ``then_norm`` when a vector joins the stream between it and the next block, or when
+    the next block's first read is left to this one (``read``, a ``FirstRead``)."""
 
-    def __init__(self, norm, offset: torch.Tensor):
-        self.norm, self.offset = norm, offset
+    def __init__(self, norm, offset: torch.Tensor | None, read: FirstRead | None = None):
+        self.norm, self.offset, self.read = norm, offset, read
 
     def row_factor_form(self):
         return None
@@ -93,16 +94,39 @@ class SandwichBlock(Block):
     def with_offset(self, then_norm, row):
         return NormThenOffset(then_norm, row) if hasattr(then_norm, "group_form") else None
 
+    def _one_kernel(self, ctx: StepContext, norm) -> bool:
+        """Whether a step's last kernel may also read for whoever comes next: every sequence brings one token (its
+        older inputs then all come from the state), and the rows are of a size that kernel keeps in registers."""
+        return bool(self.taps) and ctx.all_decode and ops.sandwich_step_conv_fits(self.hidden_size, norm.group_form()[2])
+
+    def _conv_state(self, which: int, inputs) -> torch.Tensor:
+        if self.taps < 2:     # (one tap reads no earlier input: the kernels never look at the state)
+            return self.conv_weights[which].view(1, -1)
+        return inputs.data[:, which * self.conv_floats:(which + 1) * self.conv_floats]
+
+    def first_read(self, ctx: StepContext, cache, writes_cache: bool):
+        if not self._one_kernel(ctx, self.mixer_norm):
+            return None
+        inputs = cache.get("inputs") if isinstance(cache, dict) else None
+        if self.taps > 1 and inputs is None:
+            return None
+        return FirstRead(self.conv_weights[0], self._conv_state(0, inputs), bool(writes_cache))
+
+    def with_read(self, then_norm, read):
+        if then_norm is None or read is None or not self.taps or read.weight.shape != (self.hidden_size, self.taps):
+            return then_norm
+        if isinstance(then_norm, NormThenOffset):
+            then_norm.read = read
+            return then_norm
+        return NormThenOffset(then_norm, None, read) if hasattr(then_norm, "group_form") else then_norm
+
     # ---- one run
     def _read(self, normed: torch.Tensor, which: int, ctx: StepContext, inputs, writes: bool) -> torch.Tensor:
         """h + conv(h) of the normed rows (float32), rounded to the run's type for the sublayer's first product."""
         if not self.taps:
             return normed
         out = ctx.empty(normed.shape, ctx.dtype)
-        if self.taps < 2:     # (one tap reads no earlier input: the kernel never looks at the state)
-            state = self.conv_weights[which].view(1, -1)
-        else:
-            state = inputs.data[:, which * self.conv_floats:(which + 1) * self.conv_floats]
+        state = self._conv_state(which, inputs)
         ops.causal_conv(normed, self.conv_weights[which], state, ctx.slots_dev, ctx.seq_ids, ctx.cu_seqlens, out,
                         self.hidden_size, add_input=True, update_state=writes and self.taps > 1)
         return out
@@ -116,28 +140,43 @@ class SandwichBlock(Block):
         y = ctx.extras.get("sandwich sublayer result")
         if y is None:
             y = ctx.extras["sandwich sublayer result"] = torch.zeros(residual.shape, dtype=torch.float32, device=residual.device)
-        if x_in is not None and x_in.dtype != between:
-            x_in = None      # (handed over by a block that reads differently: norm again)
-        x = x_in if x_in is not None else self.mixer_norm.forward(residual, between, alloc=ctx.empty)
-        self.mixer.forward(self._read(x, 0, ctx, inputs, writes_cache), ctx, mixer_cache, y, writes_cache)
+        if isinstance(x_in, ReadRows):
+            h = x_in.data    # (the block before this one has read for it: normed, convolved, the state moved on)
+        else:
+            if x_in is not None and x_in.dtype != between:
+                x_in = None      # (handed over by a block that reads differently: norm again)
+            x = x_in if x_in is not None else self.mixer_norm.forward(residual, between, alloc=ctx.empty)
+            h = self._read(x, 0, ctx, inputs, writes_cache)
+        self.mixer.forward(h, ctx, mixer_cache, y, writes_cache)
         last = self.mixer_out_norm
         if self.feed_forward is not None:
-            x = self._step(y, last, residual, None, self.feed_forward_norm, between, ctx.empty)
-            self.feed_forward.forward(self._read(x, 1, ctx, inputs, writes_cache), ctx, y)
+            if self._one_kernel(ctx, self.feed_forward_norm) and _agree(last, self.feed_forward_norm):
+                read = FirstRead(self.conv_weights[1], self._conv_state(1, inputs), bool(writes_cache))
+                h = self._step(y, last, residual, None, self.feed_forward_norm, between, ctx.empty, read, ctx).data
+            else:
+                h = self._read(self._step(y, last, residual, None, self.feed_forward_norm, between, ctx.empty), 1, ctx, inputs,
+                               writes_cache)
+            self.feed_forward.forward(h, ctx, y)
             last = self.feed_forward_out_norm
-        offset = None
+        offset = read = None
         if isinstance(then_norm, NormThenOffset):
-            then_norm, offset = then_norm.norm, then_norm.offset
+            then_norm, offset, read = then_norm.norm, then_norm.offset, then_norm.read
         if then_norm is not None and not (hasattr(then_norm, "group_form") and _agree(then_norm, last)):
             assert offset is None    # (with_offset only wraps norms this block can apply)
-            then_norm = None
+            then_norm = read = None
         # (rows handed to the next block outlive this block's workspace: they come from the allocator)
         return self._step(y, last, residual, offset, then_norm, between,
-                          lambda shape, dtype: torch.empty(shape, dtype=dtype, device=residual.device))
+                          lambda shape, dtype: torch.empty(shape, dtype=dtype, device=residual.device), read, ctx)
 
-    def _step(self, y, out_norm, residual, offset, next_norm, dtype, alloc):
-        """The sublayer's result into the stream; returns ``next_norm`` of the updated stream, or None without one."""
+    def _step(self, y, out_norm, residual, offset, next_norm, dtype, alloc, read: FirstRead | None = None, ctx=None):
+        """The sublayer's result into the stream; returns ``next_norm`` of the updated stream (with ``read``: a
+        ``ReadRows`` of that norm's rows read for whoever comes next), or None without a norm."""
         w, eps, groups = out_norm.group_form()
+        if read is not None and next_norm is not None and _agree(out_norm, next_norm) and self._one_kernel(ctx, next_norm):
+            out = alloc(tuple(residual.shape), ctx.dtype)
+            ops.sandwich_step_conv(y, w, self.mult, residual, eps, groups, next_norm.group_form()[0], out, read.weight,
+                                   read.state, ctx.slots_dev, offset=offset, update_state=read.writes and self.taps > 1)
+            return ReadRows(out)
         if next_norm is None:
             ops.sandwich_step(y, w, self.mult, residual, eps, groups, offset=offset)
             return None

@@ -1,6 +1,6 @@
 """Small Gatuzen configurations for the tests, and model folders with random weights made so that faults show.
 
-The three configurations differ from one another in every size and option: the order of the mixers, a loop over the
+The configurations differ from one another in every size and option: the order of the mixers, a loop over the
 first layers, over inner layers and none, one pass and several, norms in one part and in several, input convolutions of
 1 to 4 taps and none, layers without feed-forward, one expert of several and several of many, heads that share a group of
 the state-space mixer and heads that have their own, key sizes below and above value sizes, a latent plus rotated part
@@ -59,7 +59,22 @@ GATUZEN_C = {
          "mixer": {"heads": 2, "vdim": 24, "state": 40, "groups": 1, "conv": 4, "norm_groups": 3}},
     ],
 }
-CONFIGS = {"A": GATUZEN_A, "B": GATUZEN_B, "C": GATUZEN_C}
+# rows wide enough for the step kernel that keeps a token's row in registers and, in decode steps, also reads for the next
+# sublayer (groups of whole 128-number pieces): a block without feed-forward hands its rows straight to the next block,
+# and the loop's vector joins the stream in that same kernel
+GATUZEN_D = {
+    "architecture": "Gatuzen", "vocab": 120, "width": 256, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5, "groups": 2},
+    "canon": {"taps": 4}, "logit_scale": 0.8, "residual_mult": 0.5, "initializer_range": 0.05,
+    "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        {"type": "gla", "mixer": {"heads": 2, "dim": 16, "vdim": 24, "tau": 4.0, "decay_rank": 8}, "mlp": None},
+        {"type": "mamba2", "mlp": _moe(32, 3, 2),
+         "mixer": {"heads": 2, "vdim": 32, "state": 16, "groups": 2, "conv": 3, "norm_groups": 2}},
+        {"type": "latent_attention", "mlp": None, "mixer": _latent(3, 24, 8, 16, 56, 0.2)},
+        {"type": "gla", "mixer": {"heads": 1, "dim": 40, "vdim": 32, "tau": 12.0, "decay_rank": 4}, "mlp": _moe(24, 4, 1)},
+    ],
+}
+CONFIGS = {"A": GATUZEN_A, "B": GATUZEN_B, "C": GATUZEN_C, "D": GATUZEN_D}
 
 
 def make_gatuzen_dir(tmp_path: Path, config_json: dict, seed: int = 0, slow_decay: float = 3.0, edit=None) -> Path:
@@ -138,7 +153,13 @@ def assert_logits(got: torch.Tensor, ref, dtype, what: str = "") -> None:
     scale = float(ref.abs().max()) + 1e-30
     err = (got - ref).abs()
     if dtype == torch.float32:
-        assert float(err.max()) <= 5e-5 * scale, f"{what}: max err {float(err.max()):.3e} vs scale {scale:.3e}"
+        # (where one bfloat16 rounding of what the sublayers read moves the plain result far, a 32-bit rounding, 2^-15 of
+        # it, is magnified alike: such a position is allowed a few dozen of those)
+        allowed = 5e-5 * scale + (1e-3 * moved.amax(dim=-1) if moved is not None else 0.0)
+        worst = err.amax(dim=-1)
+        over = worst - allowed
+        assert float(over.max()) <= 0.0, (f"{what}: max err {float(worst.max()):.3e} vs scale {scale:.3e} "
+                                          f"(position {int(over.argmax())})")
         return
     # A sublayer's result is normed before it joins the stream, so where that result is small by chance (a recurrent
     # layer's first tokens, whose state holds one or two outer products of a few channels) the norm magnifies the

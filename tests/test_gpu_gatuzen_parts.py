@@ -38,7 +38,8 @@ def test_norm_in_groups(dtype, rows, dim, groups):
     assert torch.equal(out2.cpu(), out.cpu()[pick.long()])
 
 
-@pytest.mark.parametrize("rows, dim, groups", [(5, 48, 3), (300, 1024, 4), (3, 50, 1), (2, 2048, 1)])
+@pytest.mark.parametrize("rows, dim, groups", [(5, 48, 3), (300, 1024, 4), (3, 50, 1), (2, 2048, 1), (3, 384, 3), (4, 8192, 2),
+                                               (2, 3072, 4), (5, 1280, 2), (3, 128, 1), (2, 8320, 1)])
 @pytest.mark.parametrize("offset, follows", [(False, False), (True, True), (False, True)])
 def test_between_two_sublayers(rows, dim, groups, offset, follows):
     from gpullama3.java_b200.kernels import ops
@@ -93,6 +94,96 @@ def test_convolution_carries_its_inputs(dtype, taps, channels, bias, act, add):
             at[i] += portions[i]
     for i in range(3):
         _close(torch.cat(got[i]), refs[i], dtype, f"sequence {i}", f32=1e-5, bf16=2e-2)
+
+
+@DTYPES
+@pytest.mark.parametrize("taps, channels", [(4, 64), (2, 1024), (1, 50), (5, 36), (3, 7)])
+@pytest.mark.parametrize("form", ["added", "bias and silu", "silu alone"])
+def test_convolution_token_by_token(dtype, taps, channels, form):
+    """Three sequences: a first portion of 5, 1 and 0 tokens in one step, then one token each per step (the kernel that
+    also moves the state on), one sequence ending early and its slot taken by a new one."""
+    from gpullama3.java_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(taps + channels)
+    lens = [17, 9, 12, 6]
+    xs = [torch.randn(n, channels, generator=g).to(dtype).float() for n in lens]
+    w = torch.randn(channels, taps, generator=g)
+    b = torch.randn(channels, generator=g) if form == "bias and silu" else None
+    refs = []
+    for x in xs:
+        r = P.causal_conv(x.to(F), w.to(F), b.to(F) if b is not None else None)
+        refs.append(r + x.to(F) if form == "added" else P.silu(r))
+    state = torch.zeros(4, max(taps - 1, 1) * channels, device="cuda")
+    slot = {0: 3, 1: 0, 2: 2, 3: 0}          # sequence 3 takes sequence 1's slot when that has ended
+    got = [[] for _ in lens]
+    at = [0, 0, 0, 0]
+
+    def run(portions):
+        live = [i for i in portions if portions[i]]
+        x = torch.cat([xs[i][at[i]:at[i] + portions[i]] for i in live]).to(dtype).cuda()
+        cu = torch.tensor([0] + list(torch.tensor([portions[i] for i in live]).cumsum(0)), dtype=torch.int32).cuda()
+        seq = torch.cat([torch.full((portions[i],), j, dtype=torch.int32) for j, i in enumerate(live)]).cuda()
+        out = torch.empty_like(x)
+        kw = dict(bias=b.cuda() if b is not None else None, activation=None if form == "added" else "silu", add_input=form == "added")
+        if form == "silu alone":
+            ops.causal_conv_silu(x, w.cuda(), state, torch.tensor([slot[i] for i in live], dtype=torch.int32).cuda(), seq, cu, out, channels)
+        else:
+            ops.causal_conv(x, w.cuda(), state, torch.tensor([slot[i] for i in live], dtype=torch.int32).cuda(), seq, cu, out, channels, **kw)
+        o = 0
+        for i in live:
+            got[i].append(out[o:o + portions[i]].float().cpu())
+            o += portions[i]
+            at[i] += portions[i]
+
+    run({0: 5, 1: 1})
+    while any(at[i] < lens[i] for i in (0, 1, 2)):
+        run({i: 1 for i in (0, 1, 2) if at[i] < lens[i]})
+        if at[1] == lens[1] and at[3] == 0:
+            state[slot[3]].zero_()           # (what handing out a slot does)
+            run({3: 2})
+    while at[3] < lens[3]:
+        run({3: 1})
+    for i in range(4):
+        _close(torch.cat(got[i]), refs[i], dtype, f"sequence {i}", f32=1e-5, bf16=2e-2)
+
+
+@DTYPES
+@pytest.mark.parametrize("dim, groups, taps", [(256, 2, 4), (1024, 4, 2), (384, 1, 1), (2048, 4, 4), (1280, 2, 5), (8192, 8, 3)])
+@pytest.mark.parametrize("offset", [False, True])
+def test_step_that_reads_for_the_next_sublayer(dtype, dim, groups, taps, offset):
+    """Token by token for three sequences: the stream takes the normed result, and what the next sublayer reads is the
+    normed stream plus its convolution over the tokens so far, the older inputs kept per slot."""
+    from gpullama3.java_b200.kernels import ops
+
+    assert ops.sandwich_step_conv_fits(dim, groups)
+    g = torch.Generator().manual_seed(dim + taps)
+    n, steps = 3, 7
+    wb, wn, off = torch.randn(dim, generator=g), torch.randn(dim, generator=g), torch.randn(dim, generator=g)
+    cw = torch.randn(dim, taps, generator=g)
+    xs = torch.randn(steps, n, dim, generator=g) * 3
+    ys = torch.randn(steps, n, dim, generator=g) * 0.02
+    slots = torch.tensor([4, 1, 2], dtype=torch.int32)
+    state = torch.zeros(6, max(taps - 1, 1) * dim, device="cuda")
+    hs, outs = [], []
+    for k in range(steps):
+        xd, yd = xs[k].cuda(), ys[k].cuda()
+        out = torch.empty((n, dim), dtype=dtype, device="cuda")
+        ops.sandwich_step_conv(yd, wb.cuda(), 0.7, xd, 1e-5, groups, wn.cuda(), out, cw.cuda(), state, slots.cuda(),
+                               offset=off.cuda() if offset else None, update_state=True)
+        ref = xs[k].to(F) + 0.7 * P.grouped_rms_norm(ys[k].to(F), wb.to(F), groups, 1e-5) + (off.to(F) if offset else 0.0)
+        _close(xd, ref, torch.float32, "stream", f32=1e-6)
+        assert float(yd.abs().max()) == 0.0
+        hs.append(P.grouped_rms_norm(ref, wn.to(F), groups, 1e-5))
+        outs.append(out.float().cpu())
+    h = torch.stack(hs)                       # [steps, n, dim]
+    for i in range(n):
+        ref = h[:, i] + P.causal_conv(h[:, i], cw.to(F), None)
+        _close(torch.stack([o[i] for o in outs]), ref, dtype, f"sequence {i}", f32=1e-5, bf16=1e-2)
+    # a step that must not write leaves the state as it is
+    before = state.clone()
+    ops.sandwich_step_conv(ys[0].cuda(), wb.cuda(), 0.7, xs[0].cuda(), 1e-5, groups, wn.cuda(),
+                           torch.empty((n, dim), dtype=dtype, device="cuda"), cw.cuda(), state, slots.cuda(), update_state=False)
+    assert torch.equal(state, before)
 
 
 @DTYPES

@@ -73,7 +73,7 @@ def test_a_block_names_its_own_parts_and_nested_parameters_get_paths():
     assert set(model.parameter_specs()) == set(cfg.tensor_names())
 
 
-@pytest.mark.parametrize("change, match", [({"head_dim": 72}, "steps of 16"), ({"head_dim": 272}, "up to 256"),
+@pytest.mark.parametrize("change, match", [({"head_dim": 72}, "steps of 16"), ({"head_dim": 528}, "up to 512"),
                                            ({"head_dim": 8}, "steps of 16")])
 def test_head_sizes_no_kernel_takes_are_refused_when_the_model_is_built(change, match):
     from gpullama3.java_b200.engine.model import CausalLM
