@@ -508,7 +508,8 @@ def run_design_arm(cfg, name, args, peaks):
             engine.cache.release(s)
         slots = [engine.cache.acquire() for _ in range(batch)]
         engine.step_fn([SequenceInput(s, torch.randint(0, V, (context - 8,), generator=g).tolist(), []) for s in slots])
-        decode_kernels = kernel_table(engine, lambda: [SequenceInput(s, [1], [0]) for s in slots], False)
+        # (a token of its own for every sequence: a feed-forward routed by token id then reads as many experts as in the timed steps)
+        decode_kernels = kernel_table(engine, lambda: [SequenceInput(s, [(7919 * (i + 1)) % V], [0]) for i, s in enumerate(slots)], False)
         for s in slots:
             engine.cache.release(s)
     finally:
