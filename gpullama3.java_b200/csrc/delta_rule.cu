@@ -6,8 +6,9 @@
 //     S <- diag(g) S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q
 // in this order (the read-out sees the token's own write).  Column j of S only ever meets column j of v, u and o, so
 // the columns are independent chains:
-// a thread holds RPT rows of one column in registers (rows r, r + R, r + 2 R, ...: the R neighbouring lanes that share a
-// column read neighbouring words of shared memory), d_k <= R * RPT, rows beyond d_k are zero and stay zero, and the two
+// a thread holds RPT rows of one column in registers (four neighbouring rows per piece of 4 R rows: a lane reads them as
+// one 16-byte word, and the R neighbouring lanes that share a column read neighbouring words of shared memory),
+// d_k <= R * RPT, rows beyond d_k are zero and stay zero, and the two
 // sums over the rows that a token needs are finished by log2(R) exchanges.
 // What the chains read is made first, for all tokens at once, by delta_rule_prepare (unit norms of q and k from the
 // convolution's output, the query scale, beta = sigmoid(.), g = exp(-exp(A_log) softplus(a + dt_bias)), all 32-bit);
@@ -485,10 +486,12 @@ delta_rule_scan_kernel(ScanArgs a) {
         copy_async_commit();
     };
 
+    // register i of lane r holds row (i / 4) * 4 R + 4 r + i % 4: four neighbouring rows per lane and piece, so a lane
+    // reads them as one 16-byte word and the R lanes of a column read neighbouring words
     float S[RPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int rw = i * R + r;
+        const int rw = (i >> 2) * (4 * R) + 4 * r + (i & 3);
         S[i] = (live && rw < a.d_k) ? S_g[(size_t)rw * a.d_v + col] : 0.f;
     }
 
@@ -505,39 +508,46 @@ delta_rule_scan_kernel(ScanArgs a) {
         }
         __syncthreads();
         float* out = a.out + ((size_t)first + base) * a.heads * a.d_v + (size_t)h * a.d_v + col;
-#pragma unroll 2
+        // (without the correction a token's write does not wait for a sum over the rows: eight tokens' loads go out together)
+#pragma unroll(LINEAR ? 8 : 2)
         for (int tt = 0; tt < m; ++tt) {
-            const float* qp = buf + tt * a.row + r;
-            const float* kp = qp + dpad;
-            const float* gp = kp + dpad;
+            const float4* qp = reinterpret_cast<const float4*>(buf + tt * a.row) + r;
+            const float4* kp = qp + dpad / 4;
+            const float4* gp = kp + dpad / 4;
             const float v = buf[tt * a.row + v_at], beta = buf[tt * a.row + b_at], kq = buf[tt * a.row + b_at + 1];
             // with S' = diag(g) S:  o = (S' + k u^T)^T q = S'^T q + u (k . q), so both sums over the rows are taken from
             // S' in one pass and one round of exchanges, and k . q comes prepared with the token
-            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
+            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f}, kk[RPT];
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                S[i] *= gp[i * R];
-                d[i & 3] += S[i] * kp[i * R];
-                e[i & 3] += S[i] * qp[i * R];
+            for (int c = 0; c < RPT / 4; ++c) {
+                const float4 g4 = gp[c * R], k4 = kp[c * R], q4 = qp[c * R];
+                const float gv[4] = {g4.x, g4.y, g4.z, g4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    S[4 * c + j] *= gv[j];
+                    if constexpr (!LINEAR) d[j] += S[4 * c + j] * kv[j];
+                    e[j] += S[4 * c + j] * qv[j];
+                    kk[4 * c + j] = kv[j];
+                }
             }
             float dot = (d[0] + d[1]) + (d[2] + d[3]), read = (e[0] + e[1]) + (e[2] + e[3]);
 #pragma unroll
             for (int o = R >> 1; o > 0; o >>= 1) {
-                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if constexpr (!LINEAR) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 read += __shfl_xor_sync(0xffffffffu, read, o);
             }
             const float u = LINEAR ? beta * v : beta * (v - dot);
             if (live && r == 0)
                 out[(size_t)tt * a.heads * a.d_v] = LINEAR ? read + u * kq + buf[tt * a.row + b_at + 2] * v : read + u * kq;
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) S[i] += kp[i * R] * u;
+            for (int i = 0; i < RPT; ++i) S[i] += kk[i] * u;
         }
         __syncthreads();   // the chunk has been walked: its buffer may be filled again
         which ^= 1;
     }
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int rw = i * R + r;
+        const int rw = (i >> 2) * (4 * R) + 4 * r + (i & 3);
         if (live && rw < a.d_k) S_g[(size_t)rw * a.d_v + col] = S[i];
     }
 }
