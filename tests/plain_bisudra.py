@@ -1,0 +1,192 @@
+"""A plain, slow implementation of the Bisudra decoder: one function per mechanism, whole sequences at once,
+float64 on the CPU, no cache and no state carried between calls.  It shares no code with the package; the tests
+compare the engine with it.
+
+Notation: T tokens, x [T, width]; weights are a dict of float tensors by checkpoint name, a linear weight is
+[out, in] and is applied as x @ W.T; ``p`` is a layer's name prefix (``l3.``), ``m`` a mixer's or feed-forward's record
+of the configuration."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+F = torch.float64
+
+
+# ---------------------------------------------------------------- small functions
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def silu(z):
+    return z * torch.sigmoid(z)
+
+
+def squared_relu(z):
+    return torch.clamp(z, min=0.0) ** 2
+
+
+def over_root_mean_square(x, eps):
+    return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+
+
+def layer_norm(x, w, b, eps):
+    mean = x.mean(dim=-1, keepdim=True)
+    dev = x - mean
+    return dev / torch.sqrt((dev * dev).mean(dim=-1, keepdim=True) + eps) * w + b
+
+
+def causal_conv(h, w):
+    """y_t = sum_j w[:, j] h_(t - taps + 1 + j) per channel, zeros before the start; h [T, C], w [C, taps]."""
+    T, C = h.shape
+    taps = w.shape[1]
+    y = torch.zeros(T, C, dtype=h.dtype)
+    for t in range(T):
+        for j in range(taps):
+            s = t - taps + 1 + j
+            if s >= 0:
+                y[t] += w[:, j] * h[s]
+    return y
+
+
+def with_input_convolution(h, w):
+    return h + causal_conv(h, w)
+
+
+def residual_gate(h, w, b):
+    """What a sublayer's result is multiplied with: a sigmoid per channel of the sublayer's own input."""
+    return torch.sigmoid(h @ w.T + b)
+
+
+# ---------------------------------------------------------------- attention
+def rotate_interleaved(x, positions, base, dims):
+    """x [T, n, d]: the pairs (2i, 2i + 1), i < dims / 2, turned by position * base^(-2i / dims); the rest as it is."""
+    out = x.clone()
+    for i in range(dims // 2):
+        a = positions.to(F) * (base ** (-2.0 * i / dims))
+        c, s = torch.cos(a)[:, None], torch.sin(a)[:, None]
+        u, v = x[..., 2 * i], x[..., 2 * i + 1]
+        out[..., 2 * i] = u * c - v * s
+        out[..., 2 * i + 1] = v * c + u * s
+    return out
+
+
+def windowed_softmax_attention(q, k, v, scale, window, start=0):
+    """One head and one map: q, k [T, d], v [T, dv]; query i sees keys j with 0 <= i - j < window (window None: all
+    j <= i).  Returns [T, dv]."""
+    T = q.shape[0]
+    out = torch.zeros(T, v.shape[1], dtype=F)
+    for i in range(T):
+        lo = 0 if window is None else max(0, i - window + 1)
+        s = (k[lo:i + 1] @ q[i]) * scale
+        w = torch.softmax(s, dim=0)
+        out[i] = w @ v[lo:i + 1]
+    return out
+
+
+def differential_weight(W, p, diff):
+    return (math.exp(float((W[p + "mix.lq1"] * W[p + "mix.lk1"]).sum()))
+            - math.exp(float((W[p + "mix.lq2"] * W[p + "mix.lk2"]).sum())) + diff)
+
+
+def differential_attention(h, W, p, m, eps, positions=None):
+    """Two softmax maps per head over the same values, the second taken off the first times one number of the layer."""
+    T = h.shape[0]
+    H, G, d, dv, diff = m["heads"], m["kv_heads"], m["dim"], m["vdim"], float(m["diff"])
+    positions = torch.arange(T) if positions is None else positions
+    q = (h @ W[p + "mix.q"].T).reshape(T, H, 2, d)
+    k = (h @ W[p + "mix.k"].T).reshape(T, G, 2, d)
+    v = (h @ W[p + "mix.v"].T).reshape(T, G, dv)
+    q = over_root_mean_square(q, eps) * W[p + "mix.q.norm"]
+    k = over_root_mean_square(k, eps) * W[p + "mix.k.norm"]
+    rot = m.get("rot")
+    if rot and rot.get("dims"):
+        q = rotate_interleaved(q.reshape(T, 2 * H, d), positions, float(rot["base"]), rot["dims"]).reshape(T, H, 2, d)
+        k = rotate_interleaved(k.reshape(T, 2 * G, d), positions, float(rot["base"]), rot["dims"]).reshape(T, G, 2, d)
+    window = (m.get("mask") or {}).get("size")
+    lam = differential_weight(W, p, diff)
+    heads = []
+    for a in range(H):
+        g = a // (H // G)
+        a1 = windowed_softmax_attention(q[:, a, 0], k[:, g, 0], v[:, g], float(m["scale"]), window)
+        a2 = windowed_softmax_attention(q[:, a, 1], k[:, g, 1], v[:, g], float(m["scale"]), window)
+        o = a1 - lam * a2
+        heads.append(over_root_mean_square(o, eps) * (1.0 - diff))
+    o = torch.cat(heads, dim=1) * torch.sigmoid(h @ W[p + "mix.g"].T)
+    return o @ W[p + "mix.o"].T
+
+
+# ---------------------------------------------------------------- feed-forwards
+def dense_feed_forward(h, W, p):
+    z = squared_relu(h @ W[p + "mlp.up"].T + W[p + "mlp.up.b"])
+    return z @ W[p + "mlp.down"].T + W[p + "mlp.down.b"]
+
+
+def router_choice(h, W, p, top):
+    """Chosen experts [T, top] (largest logits first) and their weights: the softmax over the chosen logits alone."""
+    z = h @ W[p + "mlp.router"].T + W[p + "mlp.router.b"]
+    best, chosen = torch.topk(z, top, dim=-1)
+    return chosen, torch.softmax(best, dim=-1)
+
+
+def mixture_of_experts(h, W, p, mlp, choice=None):
+    chosen, weights = router_choice(h, W, p, mlp["router"]["top"]) if choice is None else choice
+    out = torch.zeros(h.shape[0], W[p + "mlp.e0.down"].shape[0], dtype=F)
+    for t in range(h.shape[0]):
+        for e, w in zip(chosen[t].tolist(), weights[t]):
+            q = f"{p}mlp.e{e}."
+            out[t] += w * ((silu(h[t] @ W[q + "gate"].T) * (h[t] @ W[q + "up"].T)) @ W[q + "down"].T)
+    return out
+
+
+def feed_forward(h, W, p, mlp):
+    return dense_feed_forward(h, W, p) if mlp["kind"] == "dense" else mixture_of_experts(h, W, p, mlp)
+
+
+# ---------------------------------------------------------------- what joins the stream beside the sublayers
+def token_side_input(x, tokens, W, p, layer, dim, eps):
+    """A few numbers per (token id, layer), gated by the stream, projected to its width and normed."""
+    e = W["side.embed"][tokens][:, layer * dim:(layer + 1) * dim]
+    g = gelu_tanh(x @ W[p + "side.gate"].T) * e
+    y = g @ W[p + "side.proj"].T
+    return over_root_mean_square(y, eps) * W[p + "side.norm"]
+
+
+def depth_average(results, w):
+    """sum_j w[j] X_j over the embedding output and every layer's result so far."""
+    return sum(w[j] * X for j, X in enumerate(results))
+
+
+# ---------------------------------------------------------------- the model
+def layer(x, tokens, W, config, i):
+    L = config["layers"][i]
+    p, eps = f"l{i}.", float(config["norm"]["eps"])
+    taps = (config.get("canon") or {}).get("taps")
+    h = with_input_convolution(x, W[p + "canon1"]) if taps else x
+    y = differential_attention(h, W, p, L["mixer"], eps) * residual_gate(x, W[p + "rg1"], W[p + "rg1.b"])
+    x = x + layer_norm(y, W[p + "norm1"], W[p + "norm1.b"], eps)
+    if L.get("mlp") is not None:
+        y = feed_forward(x, W, p, L["mlp"]) * residual_gate(x, W[p + "rg2"], W[p + "rg2.b"])
+        x = x + layer_norm(y, W[p + "norm2"], W[p + "norm2.b"], eps)
+    side = config.get("token_side")
+    if side:
+        x = x + token_side_input(x, tokens, W, p, i, side["dim"], eps)
+    return x
+
+
+def forward(config, weights, tokens, return_layers=False):
+    """Logits [T, vocab] of one sequence (float64); with ``return_layers`` also every layer's result, before the depth
+    average that follows it."""
+    W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
+    tokens = torch.as_tensor(tokens, dtype=torch.long)
+    x = W["embed"][tokens]
+    results, layers = [x], []
+    for i in range(len(config["layers"])):
+        X = layer(x, tokens, W, config, i)
+        layers.append(X)
+        results.append(X)
+        x = depth_average(results, W[f"l{i}.dwa"])
+    eps = float(config["norm"]["eps"])
+    logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["embed"].T
+    return (logits, layers) if return_layers else logits
