@@ -7,8 +7,9 @@ from .llama import LlamaConfig, RopeScaling
 from .guduzen import GuduzenConfig
 from .pekerax import PekeraxConfig
 from .gatuzen import GatuzenConfig
+from .bisudra import BisudraConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "PartSpec", "ScheduleEntry", "default_schedule",
            "read_config_json", "Architecture", "architecture_of", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture", "LlamaConfig",
-           "RopeScaling", "GuduzenConfig", "PekeraxConfig", "GatuzenConfig"]
+           "RopeScaling", "GuduzenConfig", "PekeraxConfig", "GatuzenConfig", "BisudraConfig"]

@@ -8,6 +8,9 @@
 //                      of 512 numbers and more
 //   gate_rows          x[t, :n] <- x[t, :n] * sigmoid(gate[t, :n]) (or SiLU), in place: a gate on a mixer's output
 //   scale_rows         x <- x * s, in place on 32-bit logits
+//   differential_heads out[t, h, :] = post * o / sqrt(mean(o^2) + eps) * sigmoid(gate[t, h, :]) with o = a1 - lambda a2, where
+//                      a1 and a2 are the results of two attention maps over the same values that lie as neighbouring
+//                      heads (2h, 2h + 1) of `d_pad` numbers of which the first `d` count; a warp per (token, head)
 #include "common.cuh"
 
 namespace b200 {
@@ -98,6 +101,31 @@ __global__ void gate_rows_kernel(T* __restrict__ x, int ld_x, const T* __restric
     }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(128)
+differential_heads_kernel(const T* __restrict__ maps, const T* __restrict__ gate, int ld_gate, T* __restrict__ out,
+                          int n_heads, int d, int d_pad, int n_rows, float lambda, float post, float eps) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const int t = row / n_heads, h = row % n_heads;
+    const T* a1 = maps + ((size_t)row * 2) * d_pad;
+    const T* a2 = a1 + d_pad;
+    float ss = 0.f;
+    for (int e = lane; e < d; e += 32) {
+        const float o = to_f32<T>(a1[e]) - lambda * to_f32<T>(a2[e]);
+        ss += o * o;
+    }
+    ss = warp_sum(ss);
+    const float scale = post / sqrtf(ss / (float)d + eps);
+    const T* g = gate ? gate + (size_t)t * ld_gate + (size_t)h * d : nullptr;
+    T* o_row = out + (size_t)row * d;
+    for (int e = lane; e < d; e += 32) {
+        float o = (to_f32<T>(a1[e]) - lambda * to_f32<T>(a2[e])) * scale;
+        if (g) o *= 1.0f / (1.0f + expf(-to_f32<T>(g[e])));
+        o_row[e] = from_f32<T>(o);
+    }
+}
+
 __global__ void scale_kernel(float* __restrict__ x, size_t n, float s) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= s;
 }
@@ -147,5 +175,20 @@ extern "C" int b200_scale_rows(float* x, long long n, float s, cudaStream_t stre
     if (n <= 0) return 0;
     const long long blocks = (n + 255) / 256;
     b200::scale_kernel<<<(int)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, stream>>>(x, (size_t)n, s);
+    return b200::launch_status();
+}
+
+// maps [T][2 n_heads][d_pad], gate [T][ld_gate] (or null), out [T][n_heads d], all of the run's type
+extern "C" int b200_differential_heads(const void* maps, const void* gate, int ld_gate, void* out, int dtype, int n_tokens,
+                                       int n_heads, int d, int d_pad, float lambda, float post, float eps,
+                                       cudaStream_t stream) {
+    if (n_tokens <= 0 || n_heads <= 0) return 0;
+    if (d < 1 || d_pad < d || (gate && ld_gate < n_heads * d)) return b200::kErrBadArgument;
+    const long long rows = (long long)n_tokens * n_heads;
+    if (rows > 0x7fffffffLL) return b200::kErrUnsupportedSize;
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::differential_heads_kernel<T><<<(int)((rows + 3) / 4), 128, 0, stream>>>((const T*)maps, (const T*)gate, ld_gate,
+                                                                                      (T*)out, n_heads, d, d_pad, (int)rows,
+                                                                                      lambda, post, eps));
     return b200::launch_status();
 }

@@ -1,0 +1,221 @@
+// Kernels of a block whose sublayers read the 32-bit residual stream as it is and whose results are gated, normed and
+// then added:
+//
+//   gated_norm_step    z = (y (+ yb)) * sigmoid(r + rb)                  the sublayer's result y times its gate, whose
+//                      x <- x + (z - mean(z)) / sqrt(var(z) + eps) * w + b    logits r come from a product over the
+//                      y <- 0 ;  xc = x in the run's type (optional)      sublayer's own input; a layer norm; the sum
+//   rms_add_step       x <- x + y / sqrt(mean(y^2) + eps) * w ;  y <- 0 ;  xc = x (optional)
+//   depth_average      level[n] = x ;  x <- sum_(j <= n) c[j] level[j] ;  xc = x (optional): every layer's result is
+//                      kept for the pass, and what the next layer reads is a learned mix of all of them
+//   cast_rows          xc = x in the run's type (what a product over the stream itself reads)
+//   bias_act_rows      u <- act(u + bias) in place on a product's result; act: the square of max(., 0)
+//   token_gate_rows    g[t, j] = gelu_tanh(a[t, j]) * table[token[t], j]: a few numbers per token id that the stream gates
+//
+// A CTA per token row for the three steps: a thread keeps its share of the row (the elements tid, tid + 256, ...) in
+// registers between the one fetch and the one store when the row has at most 256 * 32 numbers; longer rows are
+// evaluated again in each pass.  Mean and variance are two sums over the same kept values (the variance is the mean of
+// the squared deviations), every sum in a fixed order.  All arithmetic is 32-bit.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kStepThreads = 256;
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+struct GatedNormArgs {
+    float* y;               // [T][dim] the sublayer's result, cleared on the way out
+    const float* y_bias;    // [dim] or null
+    const void* r;          // [T][ld_r] gate logits in the run's type, or null (no gate)
+    int ld_r;
+    const float* r_bias;    // [dim] or null
+    const float* w;         // [dim]
+    const float* b;         // [dim] or null (rms form: no mean taken off, no bias)
+    float* x;               // [T][dim]
+    void* xc;               // [T][dim] in the run's type, or null
+    int dim;
+    float eps;
+    int center;             // 1: layer norm; 0: divide by the root mean square only
+};
+
+// NV > 0: the row's values stay in registers (dim <= NV * kStepThreads); NV == 0: any size, evaluated per pass.
+template <typename TR, int NV>
+__global__ void __launch_bounds__(kStepThreads)
+gated_norm_step_kernel(GatedNormArgs a) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x, dim = a.dim;
+    float* yr = a.y + (size_t)t * dim;
+    float* xr = a.x + (size_t)t * dim;
+    const TR* rr = a.r ? (const TR*)a.r + (size_t)t * a.ld_r : nullptr;
+    auto value = [&](int i) {
+        float z = yr[i] + (a.y_bias ? a.y_bias[i] : 0.f);
+        if (rr) z *= sigmoid_f(to_f32<TR>(rr[i]) + (a.r_bias ? a.r_bias[i] : 0.f));
+        return z;
+    };
+    constexpr int N = NV > 0 ? NV : 1;
+    float keep[N];
+    float sum = 0.f;
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const int i = tid + j * kStepThreads;
+            keep[j] = i < dim ? value(i) : 0.f;
+            sum += keep[j];
+        }
+    } else {
+        for (int i = tid; i < dim; i += kStepThreads) sum += value(i);
+    }
+    float mean = 0.f;
+    if (a.center) mean = block_sum(sum, scratch) / (float)dim;
+    float ss = 0.f;
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const int i = tid + j * kStepThreads;
+            const float d = i < dim ? keep[j] - mean : 0.f;
+            ss += d * d;
+        }
+    } else {
+        for (int i = tid; i < dim; i += kStepThreads) {
+            const float d = value(i) - mean;
+            ss += d * d;
+        }
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
+    TR* xc = a.xc ? (TR*)a.xc + (size_t)t * dim : nullptr;
+    auto finish = [&](int i, float z) {
+        const float v = xr[i] + ((z - mean) * scale * a.w[i] + (a.b ? a.b[i] : 0.f));
+        xr[i] = v;
+        yr[i] = 0.f;
+        if (xc) xc[i] = from_f32<TR>(v);
+    };
+    if (NV > 0) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const int i = tid + j * kStepThreads;
+            if (i < dim) finish(i, keep[j]);
+        }
+    } else {
+        for (int i = tid; i < dim; i += kStepThreads) finish(i, value(i));
+    }
+}
+
+// level[n] = x ; x <- sum_j c[j] level[j] (j = 0 .. n, in that order) ; xc = x.  Elementwise: a thread per four numbers.
+template <typename TR>
+__global__ void __launch_bounds__(256)
+depth_average_kernel(float* __restrict__ levels, size_t level_stride, int n, const float* __restrict__ c,
+                     float* __restrict__ x, TR* __restrict__ xc, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float newest = x[i];
+        levels[(size_t)n * level_stride + i] = newest;
+        float acc = 0.f;
+        for (int j = 0; j < n; ++j) acc += c[j] * levels[(size_t)j * level_stride + i];
+        acc += c[n] * newest;
+        x[i] = acc;
+        if (xc) xc[i] = from_f32<TR>(acc);
+    }
+}
+
+template <typename TR>
+__global__ void __launch_bounds__(256)
+cast_rows_kernel(const float* __restrict__ x, TR* __restrict__ xc, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        xc[i] = from_f32<TR>(x[i]);
+}
+
+template <typename TR>
+__global__ void __launch_bounds__(256)
+bias_act_rows_kernel(TR* __restrict__ u, int ld, const float* __restrict__ bias, int n) {
+    TR* ur = u + (size_t)blockIdx.x * ld;
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < n; e += gridDim.y * blockDim.x) {
+        const float z = fmaxf(to_f32<TR>(ur[e]) + (bias ? bias[e] : 0.f), 0.f);
+        ur[e] = from_f32<TR>(z * z);
+    }
+}
+
+// g[t, j] = gelu_tanh(a[t, j]) * table[token[t]][j] for j < n, zero for n <= j < width (columns a product's K is padded to)
+template <typename TR, typename TT>
+__global__ void __launch_bounds__(128)
+token_gate_rows_kernel(const TR* __restrict__ a, int ld_a, const int* __restrict__ tokens, const TT* __restrict__ table,
+                       int ld_table, int n_rows_table, TR* __restrict__ g, int ld_g, int n, int width) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= n_rows_table ? n_rows_table - 1 : tok);
+    const TT* e = table + (size_t)tok * ld_table;
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        g[(size_t)t * ld_g + j] = from_f32<TR>(j < n ? gelu_tanh_f(to_f32<TR>(a[(size_t)t * ld_a + j])) * to_f32<TT>(e[j]) : 0.f);
+}
+
+template <typename TR>
+static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t stream) {
+    const int per = (a.dim + kStepThreads - 1) / kStepThreads;
+#define B200_GATED_NORM_CASE(NV) gated_norm_step_kernel<TR, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
+    if (per <= 1) B200_GATED_NORM_CASE(1);
+    else if (per <= 2) B200_GATED_NORM_CASE(2);
+    else if (per <= 4) B200_GATED_NORM_CASE(4);
+    else if (per <= 8) B200_GATED_NORM_CASE(8);
+    else if (per <= 16) B200_GATED_NORM_CASE(16);
+    else if (per <= 32) B200_GATED_NORM_CASE(32);
+    else B200_GATED_NORM_CASE(0);
+#undef B200_GATED_NORM_CASE
+    return launch_status();
+}
+
+}  // namespace b200
+
+// `center` 1: x += layer norm of the gated result (w, b); 0: x += w * z / rms(z) (b ignored).  `r` null: no gate.
+extern "C" int b200_gated_norm_step(float* y, const float* y_bias, const void* r, int ld_r, const float* r_bias, const float* w,
+                                    const float* b, float* x, void* xc, int dtype, int n_tokens, int dim, float eps,
+                                    int center, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dim < 1 || !y || !w || !x || (r && ld_r < dim)) return b200::kErrBadArgument;
+    const b200::GatedNormArgs a = {y, y_bias, r, ld_r, r_bias, w, center ? b : nullptr, x, xc, dim, eps, center ? 1 : 0};
+    B200_DISPATCH_DTYPE(dtype, T, return b200::launch_gated_norm<T>(a, n_tokens, stream));
+    return 0;
+}
+
+// levels [>= n + 1][level_stride] 32-bit; c [n + 1] on the device; x [total] becomes the mix, its old value level n.
+extern "C" int b200_depth_average(float* levels, long long level_stride, int n, const float* c, float* x, void* xc, int dtype,
+                                  long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (n < 0 || !levels || !c || !x || level_stride < total) return b200::kErrBadArgument;
+    const long long blocks = (total + 255) / 256;
+    const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::depth_average_kernel<T><<<grid, 256, 0, stream>>>(levels, (size_t)level_stride, n, c, x, (T*)xc, (size_t)total));
+    return b200::launch_status();
+}
+
+extern "C" int b200_cast_rows(const float* x, void* xc, int dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+    B200_DISPATCH_DTYPE(dtype, T, b200::cast_rows_kernel<T><<<grid, 256, 0, stream>>>(x, (T*)xc, (size_t)total));
+    return b200::launch_status();
+}
+
+// act 0: max(u + bias, 0)^2
+extern "C" int b200_bias_act_rows(void* u, int ld, int dtype, const float* bias, int n_tokens, int n, int act,
+                                  cudaStream_t stream) {
+    if (act != 0) return b200::kErrBadArgument;
+    if (n_tokens <= 0 || n <= 0) return 0;
+    const int ny = (n + 1023) / 1024;
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::bias_act_rows_kernel<T><<<dim3(n_tokens, ny > 64 ? 64 : ny), 256, 0, stream>>>((T*)u, ld, bias, n));
+    return b200::launch_status();
+}
+
+extern "C" int b200_token_gate_rows(const void* a, int ld_a, int dtype, const int* tokens, const void* table, int table_dtype,
+                                    int ld_table, int n_rows_table, void* g, int ld_g, int n_tokens, int n, int width,
+                                    cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0) return 0;
+    if (n < 0 || n > width || ld_g < width || n_rows_table < 1) return b200::kErrBadArgument;
+    B200_DISPATCH_DTYPE(dtype, T,
+        B200_DISPATCH_DTYPE2(table_dtype, TT,
+            b200::token_gate_rows_kernel<T, TT><<<n_tokens, 128, 0, stream>>>((const T*)a, ld_a, tokens, (const TT*)table, ld_table,
+                                                                             n_rows_table, (T*)g, ld_g, n, width)));
+    return b200::launch_status();
+}

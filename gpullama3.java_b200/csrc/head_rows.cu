@@ -8,7 +8,9 @@
 //     z <- z * mul                                  (a score scale folded into the queries, or 1)
 //     z <- (1 - lambda) z + lambda other[...]       (optional: mixed with the same element of another layer's rows of the
 //                                                   same token, lambda a number in device memory; 32-bit)
-//     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes)
+//     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes; `lead` of
+//                                                   the zeros may stand in front of z, so that two rows that share a
+//                                                   wider key row each meet their own part of it)
 //     (z[2i], z[2i+1]) <- turned by position * inv_freq[i]   (optional: rotary position encoding over the row's interleaved
 //                                                   pairs, the angle, its cosine and sine in 32 bits; `mul` then also carries
 //                                                   a factor on cosine and sine)
@@ -19,14 +21,15 @@
 // A segment's rows go to a dense buffer (queries), or straight into the paged cache at the token's position: as key
 // rows ([page][kv_head][position][d_pad]) or as value rows (transposed, [page][kv_head][d_pad][position]), so that
 // a mixer without rotation needs no other kernel between its projection and attention.
-// Up to four such segments of a token's row are handled by one launch (queries, keys and values of an attention
+// Up to six such segments of a token's row are handled by one launch (queries, keys and values of an attention
 // layer; a latent that is stored once as keys and once as values).  A warp per (token, row), or a CTA per token when a
 // segment's norm runs over all its rows.
 #include "common.cuh"
 
 namespace b200 {
 
-constexpr int kRowSegments = 4;
+constexpr int kRowSegments = 6;
+constexpr int kSegmentWords = 20;   // 32-bit words of one segment record at the C interface (17 used)
 constexpr int kRowThreads = 128;
 
 struct RowSegment {
@@ -42,6 +45,7 @@ struct RowSegment {
     int src_stride;   // numbers between two rows of the source (-1: d)
     int dst_stride;   // numbers between two rows written to dst (-1: d_pad)
     int cache_dim;    // row size of the cache the segment goes into (-1: d_pad); the segment starts dst_off columns in
+    int lead;         // zeros written in front of the row: of the d_pad numbers the first `lead` are zero, then the d, then zeros
 };
 struct MixSource {
     const void* other;      // [T][ld_other], the run's storage type
@@ -101,9 +105,15 @@ __device__ __forceinline__ void head_row(const T* __restrict__ src, int ld_src, 
             step = kPageTokens;
         }
     }
+    int d_pad = g.d_pad;
+    if (g.lead > 0) {
+        for (int e = lane; e < g.lead; e += 32) o[(size_t)e * step] = from_f32<T>(0.f);
+        o += (size_t)g.lead * step;
+        d_pad -= g.lead;
+    }
     if (g.rotate) {
         const float pos = (float)cache.positions[t];
-        for (int i = lane; 2 * i < g.d_pad; i += 32) {
+        for (int i = lane; 2 * i < d_pad; i += 32) {
             float z0 = 0.f, z1 = 0.f;
             if (2 * i + 1 < g.d) {
                 const float u = (to_f32<T>(x[2 * i]) + (b ? b[2 * i] : 0.f)) * factor * (w ? w[2 * i] : 1.f);
@@ -114,11 +124,11 @@ __device__ __forceinline__ void head_row(const T* __restrict__ src, int ld_src, 
                 z1 = v * cs + u * sn;
             }
             o[(size_t)(2 * i) * step] = from_f32<T>(z0);
-            if (2 * i + 1 < g.d_pad) o[(size_t)(2 * i + 1) * step] = from_f32<T>(z1);
+            if (2 * i + 1 < d_pad) o[(size_t)(2 * i + 1) * step] = from_f32<T>(z1);
         }
         return;
     }
-    for (int e = lane; e < g.d_pad; e += 32) {
+    for (int e = lane; e < d_pad; e += 32) {
         float z = 0.f;
         if (e < g.d) {
             z = (to_f32<T>(x[e]) + (b ? b[e] : 0.f)) * factor;
@@ -186,8 +196,9 @@ head_rows_token_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ ds
 
 }  // namespace b200
 
-// `segments`: n_segments records of sixteen 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
-// weight_off, mul as float bits, target, weight_per_row, mix_off, rotate, src_stride, dst_stride, cache_dim), read on the host.  Segments with a cache target need positions, seq_ids,
+// `segments`: n_segments records of twenty 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
+// weight_off, mul as float bits, target, weight_per_row, mix_off, rotate, src_stride, dst_stride, cache_dim, lead; the rest
+// unused), read on the host.  Segments with a cache target need positions, seq_ids,
 // page_table and the pools; their n_rows is the number of kv heads of the cache entry and d_pad its head size.
 extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst, int dtype, const float* bias,
                               const float* weight, const int* segments, int n_segments, int n_tokens, float eps,
@@ -199,7 +210,7 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     b200::RowSegments segs = {};
     segs.n = n_segments;
     for (int i = 0; i < n_segments; ++i) {
-        const int* p = segments + 16 * i;
+        const int* p = segments + b200::kSegmentWords * i;
         b200::RowSegment& g = segs.seg[i];
         g.src_off = p[0]; g.n_rows = p[1]; g.d = p[2]; g.dst_off = p[3]; g.d_pad = p[4];
         g.bias_off = p[5]; g.norm = p[6]; g.weight_off = p[7];
@@ -209,7 +220,8 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
         g.target = p[9];
         g.weight_per_row = p[10];
         g.mix_off = p[11];
-        g.rotate = p[12]; g.src_stride = p[13]; g.dst_stride = p[14]; g.cache_dim = p[15];
+        g.rotate = p[12]; g.src_stride = p[13]; g.dst_stride = p[14]; g.cache_dim = p[15]; g.lead = p[16];
+        if (g.lead < 0 || g.lead + g.d > g.d_pad) return b200::kErrBadArgument;
         if (g.rotate && (!inv_freq || !positions || g.d % 2 || g.mix_off >= 0)) return b200::kErrBadArgument;
         if (g.cache_dim >= 0 && (g.target == 0 || g.dst_off < 0 || g.dst_off + g.d_pad > g.cache_dim)) return b200::kErrBadArgument;
         if (g.norm < 0 || g.norm > 2) return b200::kErrBadArgument;

@@ -1,6 +1,6 @@
 // A routed feed-forward (mixture of experts): the router, and the experts for steps of few tokens.
 //
-//   moe_route     per token: logits z = W_r h (32-bit sums, W_r kept in 32 bits), scores s = softmax(z) over all experts.
+//   moe_route     per token: logits z = W_r h (+ bias) (32-bit sums, W_r kept in 32 bits), scores s = softmax(z) over all experts.
 //                 The experts form `n_groups` equal groups of neighbours; a group's score is its best expert's score, and
 //                 only experts of the `keep_groups` best groups may be chosen.  The `top` allowed experts with the
 //                 largest scores are chosen (ties: the lower index); their weights are their scores over the sum of
@@ -72,6 +72,7 @@ struct RouteArgs {
     float* scores;          // [T][n_experts] or null: the softmax scores, for inspection
     int n_tokens, width, n_experts, n_groups, keep_groups, top;
     float norm_eps;
+    const float* bias;      // [n_experts] added to the logits, or null
 };
 
 constexpr int kRouteThreads = 128;
@@ -94,7 +95,7 @@ moe_route_kernel(RouteArgs a) {
     for (int e = warp; e < a.n_experts; e += kRouteThreads / 32) {
         const float* w = a.router + (size_t)e * a.width;
         const float z = vec ? warp_dot<float, true>(w, x, a.width, lane) : warp_dot<float, false>(w, x, a.width, lane);
-        if (lane == 0) s[e] = z;
+        if (lane == 0) s[e] = z + (a.bias ? a.bias[e] : 0.f);
     }
     __syncthreads();
     if (warp != 0) return;
@@ -500,14 +501,14 @@ extern "C" int b200_moe_table_route(const int* tokens, const int* table, int* ch
 
 extern "C" int b200_moe_route(const void* h, int ld_h, int dtype, const float* router, int* chosen, float* weights,
                               float* scores, int n_tokens, int width, int n_experts, int n_groups, int keep_groups, int top,
-                              float norm_eps, cudaStream_t stream) {
+                              float norm_eps, const float* bias, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_experts < 1 || n_experts > b200::kMaxExperts || top < 1 || top > 32 || top > n_experts || n_groups < 1 ||
         n_experts % n_groups || keep_groups < 1 || keep_groups > n_groups || top > keep_groups * (n_experts / n_groups))
         return b200::kErrBadArgument;
     const size_t smem = sizeof(float) * ((size_t)width + n_experts + n_groups);
     if (smem > 200 * 1024) return b200::kErrUnsupportedSize;
-    const b200::RouteArgs a = {h, ld_h, router, chosen, weights, scores, n_tokens, width, n_experts, n_groups, keep_groups, top, norm_eps};
+    const b200::RouteArgs a = {h, ld_h, router, chosen, weights, scores, n_tokens, width, n_experts, n_groups, keep_groups, top, norm_eps, bias};
     B200_DISPATCH_DTYPE(dtype, T,
         auto kernel = b200::moe_route_kernel<T>;
         if (smem > 48 * 1024) {

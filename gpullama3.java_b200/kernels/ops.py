@@ -111,12 +111,22 @@ _SIGNATURES = {
                                             ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_float, c_float, c_int]),
     "b200_moe_route": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_float]),
+                               c_int, c_int, c_float, c_void_p]),
     "b200_moe_rows": ("moe", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_float]),
     "b200_moe_group": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_moe_gather": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "b200_differential_heads": ("elementwise", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                c_float, c_float]),
+    "b200_gated_norm_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_float, c_int]),
+    "b200_depth_average": ("gated_residual", [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                              ctypes.c_longlong]),
+    "b200_cast_rows": ("gated_residual", [c_void_p, c_void_p, c_int, ctypes.c_longlong]),
+    "b200_bias_act_rows": ("gated_residual", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int]),
+    "b200_token_gate_rows": ("gated_residual", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                                                c_int, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -833,13 +843,13 @@ def streams_step(x: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, y: tor
 TO_ROWS, TO_CACHE_KEYS, TO_CACHE_VALUES = 0, 1, 2
 
 
-ROW_WORDS = 16   # 32-bit words of one segment record (head_rows.cu)
+ROW_WORDS = 20   # 32-bit words of one segment record (head_rows.cu: kSegmentWords)
 
 
 def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int | None = None, bias_off: int = -1,
                      norm: bool | int = False, weight_off: int = -1, mul: float = 1.0, target: int = TO_ROWS,
                      weight_per_row: bool = False, mix_off: int = -1, rotate: bool = False, src_stride: int = -1,
-                     dst_stride: int = -1, cache_dim: int = -1) -> list[int]:
+                     dst_stride: int = -1, cache_dim: int = -1, lead: int = 0) -> list[int]:
     """One segment of ``head_rows``: ``n_rows`` rows of ``d`` numbers from column ``src_off`` on, each (+ bias)
     (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on, or with
     ``target`` TO_CACHE_KEYS / TO_CACHE_VALUES into the cache page of the token's position (``n_rows`` = the cache
@@ -849,17 +859,18 @@ def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int
     token's position times ``head_rows``'s ``rotary`` frequencies (``mul`` then also carries a factor on cosine and sine).
     ``src_stride`` / ``dst_stride``: numbers between two rows read / written when they do not lie back to back (a source
     stride of 0: all rows read the same numbers).  ``cache_dim``: the row size of the cache, when the segment fills only
-    the ``d_pad`` columns from ``dst_off`` on of every cache row."""
+    the ``d_pad`` columns from ``dst_off`` on of every cache row.  ``lead``: how many of the ``d_pad`` numbers written are
+    zeros in front of the row's ``d`` (the rest of the zeros follow it)."""
     import struct
 
     return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, int(norm), weight_off,
             struct.unpack("<i", struct.pack("<f", float(mul)))[0], target, 1 if weight_per_row else 0, mix_off,
-            1 if rotate else 0, src_stride, dst_stride, cache_dim]
+            1 if rotate else 0, src_stride, dst_stride, cache_dim, int(lead), 0, 0, 0]
 
 
 def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
               weight: torch.Tensor | None = None, cache=None, mix=None, rotary=None) -> None:
-    """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments).  ``cache``: (positions,
+    """``segments``: a ctypes array made by ``head_row_segments`` (at most six segments).  ``cache``: (positions,
     seq_ids, page_table, k_pool, v_pool) for segments that go into the paged cache; ``dst`` may be None when all do.
     ``mix``: (other [T, >= ...] of src's dtype, lambda float32 [1]) for segments with a ``mix_off``.  ``rotary``:
     (positions int32 [T], inverse frequencies float32 [>= d / 2]) for segments that rotate."""
@@ -942,6 +953,84 @@ def scale_rows(logits: torch.Tensor, scale: float) -> None:
     _dev(logits)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     _check(_fn("b200_scale_rows")(logits.data_ptr(), logits.numel(), float(scale), _stream()), "scale_rows")
+
+
+def differential_heads(maps: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, n_heads: int, d: int, d_pad: int,
+                       weight: float, post: float, eps: float) -> None:
+    """maps [T, 2 n_heads d_pad]: heads (2h, 2h + 1) are two attention maps' results over the same values.  out[t, h] =
+    post * o / sqrt(mean(o^2) + eps) * sigmoid(gate[t, h]) over the first ``d`` numbers, o = map 1 - weight * map 2."""
+    _dev(maps, gate, out)
+    assert maps.is_contiguous() and out.is_contiguous() and maps.dtype == out.dtype
+    assert maps.shape[1] == 2 * n_heads * d_pad and out.shape[1] == n_heads * d and maps.shape[0] == out.shape[0]
+    assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads * d)
+    _check(_fn("b200_differential_heads")(maps.data_ptr(), gate.data_ptr() if gate is not None else None,
+                                          gate.stride(0) if gate is not None else 0, out.data_ptr(), dtype_code(out.dtype),
+                                          out.shape[0], int(n_heads), int(d), int(d_pad), float(weight), float(post), float(eps),
+                                          _stream()), "differential_heads")
+
+
+# --------------------------------------------------------------------------- a block that gates and norms what its sublayers return
+def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, x: torch.Tensor, eps: float, *,
+                    gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None,
+                    y_bias: torch.Tensor | None = None, cast: torch.Tensor | None = None, center: bool = True) -> None:
+    """z = (y (+ y_bias)) * sigmoid(gate (+ gate_bias)); x <- x + layer_norm(z) * weight + bias (``center`` False: x <- x +
+    weight * z / rms(z)); y <- 0; ``cast`` receives the new x in its own type.  x, y [T, dim], the vectors float32;
+    ``gate`` [T, >= dim] in the run's type (None: no gate)."""
+    _dev(y, weight, bias, x, gate, gate_bias, y_bias, cast)
+    T, dim = x.shape
+    assert x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
+    for v in (weight, bias, gate_bias, y_bias):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == dim)
+    assert gate is None or (gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= dim)
+    assert cast is None or (cast.is_contiguous() and cast.shape == x.shape)
+    assert gate is None or cast is None or gate.dtype == cast.dtype
+    run = gate.dtype if gate is not None else (cast.dtype if cast is not None else torch.float32)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(_fn("b200_gated_norm_step")(y.data_ptr(), ptr(y_bias), ptr(gate), gate.stride(0) if gate is not None else 0,
+                                       ptr(gate_bias), weight.data_ptr(), ptr(bias), x.data_ptr(), ptr(cast), dtype_code(run),
+                                       T, dim, float(eps), 1 if center else 0, _stream()), "gated_norm_step")
+
+
+def depth_average(levels: torch.Tensor, n: int, coefficients: torch.Tensor, x: torch.Tensor,
+                  cast: torch.Tensor | None = None) -> None:
+    """levels[n] = x; x <- sum_(j <= n) coefficients[j] levels[j]; ``cast`` receives the new x in its own type.
+    levels float32 [>= n + 1, T, dim], x float32 [T, dim], coefficients float32 [n + 1] on the device."""
+    _dev(levels, coefficients, x, cast)
+    assert levels.dtype == x.dtype == coefficients.dtype == torch.float32 and levels.is_contiguous() and x.is_contiguous()
+    assert levels.shape[0] > n >= 0 and tuple(levels.shape[1:]) == tuple(x.shape) and coefficients.numel() == n + 1
+    assert coefficients.is_contiguous() and (cast is None or (cast.is_contiguous() and cast.shape == x.shape))
+    _check(_fn("b200_depth_average")(levels.data_ptr(), levels.stride(0), int(n), coefficients.data_ptr(), x.data_ptr(),
+                                     cast.data_ptr() if cast is not None else None,
+                                     dtype_code(cast.dtype) if cast is not None else F32, x.numel(), _stream()), "depth_average")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in out's type."""
+    _dev(x, out)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.shape == out.shape
+    _check(_fn("b200_cast_rows")(x.data_ptr(), out.data_ptr(), dtype_code(out.dtype), x.numel(), _stream()), "cast_rows")
+
+
+UNGATED_ACTIVATIONS = {"relu_squared": 0}
+
+
+def bias_act_rows(u: torch.Tensor, bias: torch.Tensor | None, activation: str = "relu_squared") -> None:
+    """u <- act(u + bias) in place on a product's result [T, n]; ``relu_squared``: max(., 0)^2, evaluated in 32 bits."""
+    _dev(u, bias)
+    assert u.stride(1) == 1 and (bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == u.shape[1]))
+    _check(_fn("b200_bias_act_rows")(u.data_ptr(), u.stride(0), dtype_code(u.dtype), bias.data_ptr() if bias is not None else None,
+                                     u.shape[0], u.shape[1], UNGATED_ACTIVATIONS[activation], _stream()), "bias_act_rows")
+
+
+def token_gate_rows(a: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, n: int) -> None:
+    """out[t, j] = gelu_tanh(a[t, j]) * table[tokens[t], j] for j < n, 0 for the further columns of out."""
+    _dev(a, tokens, table, out)
+    assert a.dtype == out.dtype and a.stride(1) == 1 and out.stride(1) == 1 and table.stride(1) == 1
+    assert tokens.dtype == torch.int32 and tokens.numel() == a.shape[0] == out.shape[0]
+    assert a.shape[1] >= n and table.shape[1] >= n and out.shape[1] >= n
+    _check(_fn("b200_token_gate_rows")(a.data_ptr(), a.stride(0), dtype_code(a.dtype), tokens.data_ptr(), table.data_ptr(),
+                                       dtype_code(table.dtype), table.stride(0), table.shape[0], out.data_ptr(), out.stride(0),
+                                       a.shape[0], int(n), out.shape[1], _stream()), "token_gate_rows")
 
 
 # --------------------------------------------------------------------------- norms in groups, and a block that norms both ways
@@ -1133,8 +1222,8 @@ MAX_EXPERTS, MAX_EXPERTS_PER_TOKEN = 1024, 32   # moe.cu
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, n_groups: int,
-              keep_groups: int, norm_eps: float, scores: torch.Tensor | None = None) -> None:
-    """Per token of h [T, width]: softmax scores over router [E, width] (float32), the ``top`` = chosen.shape[1] best
+              keep_groups: int, norm_eps: float, scores: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
+    """Per token of h [T, width]: softmax scores over router [E, width] (float32; ``bias`` float32 [E] joins the logits), the ``top`` = chosen.shape[1] best
     experts among the ``keep_groups`` best of ``n_groups`` groups of neighbours into chosen int32 [T, top], and
     their scores over the chosen scores' sum (+ norm_eps) into weights float32 [T, top]."""
     _dev(h, router, chosen, weights, scores)
@@ -1144,9 +1233,12 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weigh
     assert chosen.dtype == torch.int32 and weights.dtype == torch.float32 and chosen.is_contiguous() and weights.is_contiguous()
     assert chosen.shape == weights.shape and chosen.shape[0] == T
     assert scores is None or (scores.dtype == torch.float32 and scores.is_contiguous() and tuple(scores.shape) == (T, E))
+    _dev(bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == E)
     _check(_fn("b200_moe_route")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), router.data_ptr(), chosen.data_ptr(),
                                  weights.data_ptr(), scores.data_ptr() if scores is not None else None, T, width, E,
-                                 int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps), _stream()), "moe_route")
+                                 int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps),
+                                 bias.data_ptr() if bias is not None else None, _stream()), "moe_route")
 
 
 def moe_table_route(tokens: torch.Tensor, table: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,

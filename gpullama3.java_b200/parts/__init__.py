@@ -17,6 +17,9 @@ from .routed_feed_forward import RoutedFeedForward
 from .linear_recurrence import GatedLinearAttention, StateSpaceDuality
 from .sandwich import SandwichBlock
 from .position import YarnRotaryPositionEncoding
+from .feed_forward import DenseFeedForward
+from .differential_attention import DifferentialAttention
+from .gated_residual import GatedResidualBlock
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PartRegistryError", "PositionEncoding", "ScaledRows",
            "StepContext", "all_parts", "build_block", "build_part", "register_block", "register_feed_forward",
@@ -24,4 +27,5 @@ __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PartRegistryError",
            "RotaryPositionEncoding", "llama3_inverse_frequencies", "GroupedQueryAttention", "SwiGLUFeedForward",
            "PreNormBlock", "OutputHead", "TokenEmbedding", "ConnectedBlock", "StreamConnection", "LatentAttention",
            "ChannelDeltaRule", "HeadDeltaRule", "LayerNorm", "RoutedFeedForward", "GatedLinearAttention",
-           "StateSpaceDuality", "SandwichBlock", "YarnRotaryPositionEncoding"]
+           "StateSpaceDuality", "SandwichBlock", "YarnRotaryPositionEncoding", "DenseFeedForward",
+           "DifferentialAttention", "GatedResidualBlock"]

@@ -118,16 +118,8 @@ class GroupedQueryAttention(Mixer):
         return KVCacheNeed(self.n_kv_heads, self.head_dim, self.cache_window, self.keep_first if self.cache_window else 0)
 
     def plan_decode(self, ctx: StepContext, cache: KVView) -> tuple[int, bool]:
-        """How a decode step's attention is launched: into how many spans each sequence's keys are cut, and
-        whether the kernel may be scheduled while its predecessor still runs.  Both follow from the number of
-        sequences, this mixer's own kv heads and the longest sequence the step must be right for (its cache
-        group's ``kv_capacity``: a recorded step is replayed until its page tables are outgrown)."""
-        capacity = ctx.capacity(cache.group)
-        if self.window:
-            capacity = min(capacity, self.window + self.keep_first)
-        resident = ops.resident_ctas(ctx.device, self.head_dim, self.n_heads // self.n_kv_heads)
-        splits = ops.attention_decode_splits(ctx.n_seqs, self.n_kv_heads, capacity, resident)
-        return splits, ops.attention_decode_early_start(ctx.n_seqs, self.n_kv_heads, capacity, splits)
+        """How a decode step's attention is launched (``plan_decode_attention``)."""
+        return plan_decode_attention(self, ctx, cache)
 
     def load(self, tensors, dtype, device):
         if self.finishes_heads:
@@ -230,15 +222,39 @@ class GroupedQueryAttention(Mixer):
                                      cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
                                      self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
         gate = raw[:, self.gate_off:self.gate_off + self.n_heads] if self.output_gate else None
-        if not attended and not fast.try_attention(qkv, out, ctx, table, cache, self, gate):
-            # (the plain kernel: a step of few tokens cuts their keys into spans so that the GPU has CTAs to run)
-            rows = x.shape[0] * self.n_heads
-            reach = ctx.capacity(cache.group) if not self.window else min(ctx.capacity(cache.group), self.window + self.keep_first)
-            splits = 1 if rows >= 1024 else max(1, min(16, 1024 // rows, reach // 512))
-            ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
-                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0, n_splits=splits,
-                                keep_first=self.keep_first, slopes=self.slopes, sinks=self.sinks, gate=gate)
+        if not attended:
+            attend(self, qkv, out, ctx, table, cache, gate)
         return self.o.add_to(out, residual, then_norm)
+
+
+def plan_decode_attention(shape, ctx: StepContext, cache: KVView) -> tuple[int, bool]:
+    """How a decode step's attention is launched: into how many spans each sequence's keys are cut, and
+    whether the kernel may be scheduled while its predecessor still runs.  Both follow from the number of
+    sequences, the mixer's own kv heads and the longest sequence the step must be right for (its cache
+    group's ``kv_capacity``: a recorded step is replayed until its page tables are outgrown).  ``shape``: whatever
+    has ``n_heads``, ``n_kv_heads``, ``head_dim``, ``window`` and ``keep_first`` as the attention kernels are to see them."""
+    capacity = ctx.capacity(cache.group)
+    if shape.window:
+        capacity = min(capacity, shape.window + shape.keep_first)
+    resident = ops.resident_ctas(ctx.device, shape.head_dim, shape.n_heads // shape.n_kv_heads)
+    splits = ops.attention_decode_splits(ctx.n_seqs, shape.n_kv_heads, capacity, resident)
+    return splits, ops.attention_decode_early_start(ctx.n_seqs, shape.n_kv_heads, capacity, splits)
+
+
+def attend(shape, qkv: torch.Tensor, out: torch.Tensor, ctx: StepContext, table: torch.Tensor, cache: KVView, gate=None) -> None:
+    """Attention of the finished query rows in ``qkv`` over the paged cache into ``out``: a tensor-core kernel where one
+    takes the sizes, else the plain kernel (a step of few tokens cuts their keys into spans so that the GPU has CTAs to
+    run).  ``shape`` as for ``plan_decode_attention``, with ``plan_decode``, ``has_terms`` and the terms themselves
+    (``slopes``, ``sinks``) where it has any."""
+    if fast.try_attention(qkv, out, ctx, table, cache, shape, gate):
+        return
+    rows = qkv.shape[0] * shape.n_heads
+    reach = ctx.capacity(cache.group) if not shape.window else min(ctx.capacity(cache.group), shape.window + shape.keep_first)
+    splits = 1 if rows >= 1024 else max(1, min(16, 1024 // rows, reach // 512))
+    ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
+                        shape.n_heads, shape.n_kv_heads, shape.head_dim, shape.window or 0, n_splits=splits,
+                        keep_first=shape.keep_first, slopes=getattr(shape, "slopes", None), sinks=getattr(shape, "sinks", None),
+                        gate=gate)
 
 
 VALUE_MIX_SOURCE = "value mix source"   # in a pass's ``ctx.extras``: the first value-mixing layer's own values [T, G dv]

@@ -5,6 +5,9 @@
     ``keep_groups`` best groups can be chosen; the ``top`` best of those are
     y = sum over the chosen e of  s_e / (sum of the chosen s + 1e-20) * down_e( act(gate_e h, up_e h) )
 
+With ``router_bias`` a learned vector joins the logits z.  With one group and ``weight_eps`` 0 the weights are the softmax
+over the chosen logits alone (s_e over the chosen s is exp(z_e) over the chosen exp(z)).
+
 With ``router="table"`` there is no router product: row ``token id`` of an integer table [vocabulary, top] names the token's
 experts, and every one of them weighs 1 / top.
 
@@ -33,13 +36,16 @@ class RoutedFeedForward(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int, top: int, groups: int = 1,
                  keep_groups: int | None = None, activation: str = "silu", limit: float | None = None, slope: float = 1.0,
-                 weight_eps: float = 1e-20, router: str = "learned", vocab_size: int | None = None):
+                 weight_eps: float = 1e-20, router: str = "learned", vocab_size: int | None = None,
+                 router_bias: bool = False):
         keep_groups = groups if keep_groups is None else keep_groups
         if router not in ("learned", "table"):
             raise ConfigError(f"routed feed-forward: router {router!r}; known: learned, table")
         if router == "table" and not vocab_size:
             raise ConfigError("routed feed-forward: a routing table needs the vocabulary's size")
-        self.routing, self.vocab_size = router, int(vocab_size or 0)
+        if router_bias and router != "learned":
+            raise ConfigError("routed feed-forward: only a learned router has logits a bias can join")
+        self.routing, self.vocab_size, self.router_bias = router, int(vocab_size or 0), bool(router_bias)
         if activation not in ops.ACTIVATION_CODES:
             raise ConfigError(f"feed-forward activation {activation!r}; known: {', '.join(sorted(ops.ACTIVATION_CODES))}")
         if activation == "clamped_sigmoid" and (limit is None or not limit > 0):
@@ -59,6 +65,8 @@ class RoutedFeedForward(FeedForward):
     def parameters(self):
         p = ({"router": ParamSpec((self.n_experts, self.hidden_size))} if self.routing == "learned" else
              {"table": ParamSpec((self.vocab_size, self.top), "int_table", float(self.n_experts))})
+        if self.router_bias:
+            p["router_bias"] = ParamSpec((self.n_experts,), "normal", 0.0, 0.02)
         for e in range(self.n_experts):
             p[f"e{e}.gate"] = ParamSpec((self.intermediate_size, self.hidden_size))
             p[f"e{e}.up"] = ParamSpec((self.intermediate_size, self.hidden_size))
@@ -70,6 +78,7 @@ class RoutedFeedForward(FeedForward):
         E, ff, h = self.n_experts, self.intermediate_size, self.hidden_size
         if self.routing == "learned":
             self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+            self.bias = tensors["router_bias"].to(device=device, dtype=torch.float32).contiguous() if self.router_bias else None
         else:
             self.table = tensors["table"].to(device=device, dtype=torch.int32).contiguous()
         self.w_gate_up = torch.empty((E, 2 * ff, h), dtype=run, device=device)   # gate and up rows interleaved
@@ -92,7 +101,7 @@ class RoutedFeedForward(FeedForward):
         if self.routing == "table":
             ops.moe_table_route(ctx.tokens, self.table, chosen, weights, self.n_experts)
             return chosen, weights
-        ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores)
+        ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores, self.bias)
         return chosen, weights
 
     def as_prompt(self, ctx: StepContext, n_tokens: int) -> bool:
