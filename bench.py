@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--batch 8] [--context 4096] [--layers L] [--sizes all|none]
-    python bench.py --design guduzen|pekerax|gatuzen [--design-sizes s,m]     (another workload, see the end of this text)
+    python bench.py --design guduzen|pekerax|gatuzen|bisudra [--design-sizes s,m]     (another workload, see the end of this text)
 
 Default run: the Llama-3.2-1B shape (BASELINE.json configs[2]) with random bfloat16 weights, a
 batch of 8 sequences at context length 4096.  A "step" is one decode step.  ``value`` is decoded
@@ -36,6 +36,13 @@ mixer, latent attention with a rotated shared key part and an output gate; every
 4-tap input convolution; every feed-forward routed by a table from token id to experts: 8 experts of half the dense
 width, 2 per token) beside the Pekerax decoder, the closest existing model (delta rule on the same scan, routed
 feed-forward), and the Guduzen decoder (latent attention, delta rule), all of equal width, depth and heads.
+
+``--design bisudra`` does the same for the Bisudra decoder (differential attention: half as many heads, each with two
+maps of 64 over values of 128, a window, a gate on the heads' results; sublayers that read the stream itself and are
+gated and layer-normed on their way back into it; a 4-tap input convolution; 64 numbers per token id and layer that join
+the stream; every layer's result mixed with all earlier ones; feed-forwards dense and routed in turn, 8 experts of half
+the dense width, 2 per token) beside the Pekerax decoder, the closest existing model (window attention with an output
+gate, layer norms, dense and routed feed-forwards), and the Llama 3 decoder, all of equal width, depth and projections.
 
 The library runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """
@@ -460,6 +467,19 @@ def gatuzen_config(z):
             "layers": layers}
 
 
+def bisudra_config(z):
+    """Differential attention with half the heads (two maps of `dim` each, values of twice `dim`: the projections have
+    the sizes of the other decoders'), a window, rotation of half of every map; feed-forwards dense and routed in turn
+    (8 experts of half the dense width, 2 per token)."""
+    att = {"heads": z["heads"] // 2, "kv_heads": max(1, z["kv_heads"] // 2), "dim": z["dim"], "vdim": 2 * z["dim"],
+           "scale": z["dim"] ** -0.5, "diff": 0.35, "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["dim"] // 2}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2}, "router": {"experts": 8, "top": 2}}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": dense if i % 2 == 0 else moe} for i in range(z["layers"])]
+    return {"architecture": "Bisudra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "token_side": {"dim": 64}, "layers": layers}
+
+
 def llama_like(z):
     return {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -541,6 +561,10 @@ DESIGNS = {
     "gatuzen": (gatuzen_config, "Gatuzen, layers gated linear attention / state-space mixer / latent attention with a "
                                 "rotated shared key part, sublayers normed on both sides behind input convolutions, "
                                 "feed-forwards routed by table (8 experts, 2 per token)", ("pekerax", "guduzen")),
+    "bisudra": (bisudra_config, "Bisudra, differential attention with a window and an output gate, sublayers gated and "
+                                "layer-normed into the stream, input convolution, token input, every layer's result "
+                                "mixed with the earlier ones, feed-forwards dense and routed in turn (8 experts, 2 per "
+                                "token)", ("pekerax", "llama")),
 }
 
 

@@ -29,7 +29,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 struct GatedNormArgs {
     float* y;               // [T][dim] the sublayer's result, cleared on the way out
     const float* y_bias;    // [dim] or null
-    const void* r;          // [T][ld_r] gate logits in the run's type, or null (no gate)
+    const void* r;          // [T][ld_r] gate logits (32-bit or the run's type), or null (no gate)
     int ld_r;
     const float* r_bias;    // [dim] or null
     const float* w;         // [dim]
@@ -42,7 +42,7 @@ struct GatedNormArgs {
 };
 
 // NV > 0: the row's values stay in registers (dim <= NV * kStepThreads); NV == 0: any size, evaluated per pass.
-template <typename TR, int NV>
+template <typename TR, typename TC, int NV>
 __global__ void __launch_bounds__(kStepThreads)
 gated_norm_step_kernel(GatedNormArgs a) {
     __shared__ float scratch[33];
@@ -85,12 +85,12 @@ gated_norm_step_kernel(GatedNormArgs a) {
         }
     }
     const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
-    TR* xc = a.xc ? (TR*)a.xc + (size_t)t * dim : nullptr;
+    TC* xc = a.xc ? (TC*)a.xc + (size_t)t * dim : nullptr;
     auto finish = [&](int i, float z) {
         const float v = xr[i] + ((z - mean) * scale * a.w[i] + (a.b ? a.b[i] : 0.f));
         xr[i] = v;
         yr[i] = 0.f;
-        if (xc) xc[i] = from_f32<TR>(v);
+        if (xc) xc[i] = from_f32<TC>(v);
     };
     if (NV > 0) {
 #pragma unroll
@@ -149,10 +149,10 @@ token_gate_rows_kernel(const TR* __restrict__ a, int ld_a, const int* __restrict
         g[(size_t)t * ld_g + j] = from_f32<TR>(j < n ? gelu_tanh_f(to_f32<TR>(a[(size_t)t * ld_a + j])) * to_f32<TT>(e[j]) : 0.f);
 }
 
-template <typename TR>
+template <typename TR, typename TC>
 static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t stream) {
     const int per = (a.dim + kStepThreads - 1) / kStepThreads;
-#define B200_GATED_NORM_CASE(NV) gated_norm_step_kernel<TR, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
+#define B200_GATED_NORM_CASE(NV) gated_norm_step_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
     if (per <= 1) B200_GATED_NORM_CASE(1);
     else if (per <= 2) B200_GATED_NORM_CASE(2);
     else if (per <= 4) B200_GATED_NORM_CASE(4);
@@ -167,13 +167,14 @@ static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t 
 }  // namespace b200
 
 // `center` 1: x += layer norm of the gated result (w, b); 0: x += w * z / rms(z) (b ignored).  `r` null: no gate.
-extern "C" int b200_gated_norm_step(float* y, const float* y_bias, const void* r, int ld_r, const float* r_bias, const float* w,
-                                    const float* b, float* x, void* xc, int dtype, int n_tokens, int dim, float eps,
-                                    int center, cudaStream_t stream) {
+// `r_dtype`: the gate logits' type; `dtype`: that of xc.
+extern "C" int b200_gated_norm_step(float* y, const float* y_bias, const void* r, int ld_r, int r_dtype, const float* r_bias,
+                                    const float* w, const float* b, float* x, void* xc, int dtype, int n_tokens, int dim,
+                                    float eps, int center, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dim < 1 || !y || !w || !x || (r && ld_r < dim)) return b200::kErrBadArgument;
     const b200::GatedNormArgs a = {y, y_bias, r, ld_r, r_bias, w, center ? b : nullptr, x, xc, dim, eps, center ? 1 : 0};
-    B200_DISPATCH_DTYPE(dtype, T, return b200::launch_gated_norm<T>(a, n_tokens, stream));
+    B200_DISPATCH_DTYPE(r_dtype, TR, B200_DISPATCH_DTYPE2(dtype, TC, return b200::launch_gated_norm<TR, TC>(a, n_tokens, stream)));
     return 0;
 }
 

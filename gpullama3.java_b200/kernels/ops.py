@@ -119,7 +119,7 @@ _SIGNATURES = {
     "b200_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_differential_heads": ("elementwise", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                                 c_float, c_float]),
-    "b200_gated_norm_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+    "b200_gated_norm_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_void_p, c_int, c_int, c_int, c_float, c_int]),
     "b200_depth_average": ("gated_residual", [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               ctypes.c_longlong]),
@@ -975,7 +975,7 @@ def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
                     y_bias: torch.Tensor | None = None, cast: torch.Tensor | None = None, center: bool = True) -> None:
     """z = (y (+ y_bias)) * sigmoid(gate (+ gate_bias)); x <- x + layer_norm(z) * weight + bias (``center`` False: x <- x +
     weight * z / rms(z)); y <- 0; ``cast`` receives the new x in its own type.  x, y [T, dim], the vectors float32;
-    ``gate`` [T, >= dim] in the run's type (None: no gate)."""
+    ``gate`` [T, >= dim], float32 or bfloat16 (None: no gate)."""
     _dev(y, weight, bias, x, gate, gate_bias, y_bias, cast)
     T, dim = x.shape
     assert x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
@@ -983,11 +983,10 @@ def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == dim)
     assert gate is None or (gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= dim)
     assert cast is None or (cast.is_contiguous() and cast.shape == x.shape)
-    assert gate is None or cast is None or gate.dtype == cast.dtype
-    run = gate.dtype if gate is not None else (cast.dtype if cast is not None else torch.float32)
     ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_gated_norm_step")(y.data_ptr(), ptr(y_bias), ptr(gate), gate.stride(0) if gate is not None else 0,
-                                       ptr(gate_bias), weight.data_ptr(), ptr(bias), x.data_ptr(), ptr(cast), dtype_code(run),
+                                       dtype_code(gate.dtype) if gate is not None else F32, ptr(gate_bias), weight.data_ptr(),
+                                       ptr(bias), x.data_ptr(), ptr(cast), dtype_code(cast.dtype) if cast is not None else F32,
                                        T, dim, float(eps), 1 if center else 0, _stream()), "gated_norm_step")
 
 

@@ -15,8 +15,8 @@ of what a run of the block keeps per sequence (32-bit, beside the mixer's cache)
 the block is built with (layer norms with weight and bias, or RMS norms); the gates read the sublayer's own input before
 the convolution.  A sublayer's last product adds into a 32-bit row buffer of the pass; one kernel then gates and norms
 that result into the stream, clears the buffer and leaves the updated stream in the run's type for the products that
-read it next (the gate's, the feed-forward's, the next block's).  The stream, the gates' sigmoid, the norms, the
-convolution with its state and the mix over the levels are 32-bit in both precisions."""
+read it next (the gate's, the feed-forward's, the next block's).  The stream, the gates' logits and sigmoid, the norms,
+the convolution with its state and the mix over the levels are 32-bit in both precisions."""
 from __future__ import annotations
 
 import torch
@@ -201,7 +201,7 @@ class GatedResidualBlock(Block):
         stream; returns ``cast``, which then holds the updated stream in the run's type."""
         bias = getattr(norm, "bias", None)
         w = norm.weight if norm.weight.dtype == torch.float32 else norm.group_form()[0]
-        r = self.gates[which].store(x, ctx.dtype, ctx.empty)
+        r = self.gates[which].store(x, torch.float32, ctx.empty)    # (the gate's logits leave their product in 32 bits)
         ops.gated_norm_step(y, w, bias, residual, norm.eps, gate=r, gate_bias=self.gate_biases[which], y_bias=y_bias, cast=cast,
                             center=bias is not None)
         return cast

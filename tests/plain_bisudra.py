@@ -15,6 +15,15 @@ F = torch.float64
 
 
 # ---------------------------------------------------------------- small functions
+_ROUNDING = [None]   # a function applied to what every product reads and returns while ``forward(..., reads=f)`` runs
+
+
+def product(x, w):
+    """x @ w.T; while a rounding is set, of the rounded x, and rounded itself."""
+    f = _ROUNDING[0]
+    return x @ w.T if f is None else f(f(x) @ w.T)
+
+
 def gelu_tanh(z):
     return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
@@ -41,12 +50,10 @@ def causal_conv(h, w):
     """y_t = sum_j w[:, j] h_(t - taps + 1 + j) per channel, zeros before the start; h [T, C], w [C, taps]."""
     T, C = h.shape
     taps = w.shape[1]
+    padded = torch.cat([torch.zeros(taps - 1, C, dtype=h.dtype), h], dim=0)
     y = torch.zeros(T, C, dtype=h.dtype)
-    for t in range(T):
-        for j in range(taps):
-            s = t - taps + 1 + j
-            if s >= 0:
-                y[t] += w[:, j] * h[s]
+    for j in range(taps):
+        y = y + padded[j:j + T] * w[:, j]
     return y
 
 
@@ -56,7 +63,7 @@ def with_input_convolution(h, w):
 
 def residual_gate(h, w, b):
     """What a sublayer's result is multiplied with: a sigmoid per channel of the sublayer's own input."""
-    return torch.sigmoid(h @ w.T + b)
+    return torch.sigmoid(product(h, w) + b)
 
 
 # ---------------------------------------------------------------- attention
@@ -72,17 +79,15 @@ def rotate_interleaved(x, positions, base, dims):
     return out
 
 
-def windowed_softmax_attention(q, k, v, scale, window, start=0):
+def windowed_softmax_attention(q, k, v, scale, window):
     """One head and one map: q, k [T, d], v [T, dv]; query i sees keys j with 0 <= i - j < window (window None: all
     j <= i).  Returns [T, dv]."""
     T = q.shape[0]
-    out = torch.zeros(T, v.shape[1], dtype=F)
-    for i in range(T):
-        lo = 0 if window is None else max(0, i - window + 1)
-        s = (k[lo:i + 1] @ q[i]) * scale
-        w = torch.softmax(s, dim=0)
-        out[i] = w @ v[lo:i + 1]
-    return out
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    seen = (j <= i) if window is None else ((j <= i) & (i - j < window))
+    s = (q @ k.T) * scale
+    s = torch.where(seen, s, torch.full_like(s, -math.inf))
+    return torch.softmax(s, dim=-1) @ v
 
 
 def differential_weight(W, p, diff):
@@ -95,9 +100,9 @@ def differential_attention(h, W, p, m, eps, positions=None):
     T = h.shape[0]
     H, G, d, dv, diff = m["heads"], m["kv_heads"], m["dim"], m["vdim"], float(m["diff"])
     positions = torch.arange(T) if positions is None else positions
-    q = (h @ W[p + "mix.q"].T).reshape(T, H, 2, d)
-    k = (h @ W[p + "mix.k"].T).reshape(T, G, 2, d)
-    v = (h @ W[p + "mix.v"].T).reshape(T, G, dv)
+    q = product(h, W[p + "mix.q"]).reshape(T, H, 2, d)
+    k = product(h, W[p + "mix.k"]).reshape(T, G, 2, d)
+    v = product(h, W[p + "mix.v"]).reshape(T, G, dv)
     q = over_root_mean_square(q, eps) * W[p + "mix.q.norm"]
     k = over_root_mean_square(k, eps) * W[p + "mix.k.norm"]
     rot = m.get("rot")
@@ -113,14 +118,14 @@ def differential_attention(h, W, p, m, eps, positions=None):
         a2 = windowed_softmax_attention(q[:, a, 1], k[:, g, 1], v[:, g], float(m["scale"]), window)
         o = a1 - lam * a2
         heads.append(over_root_mean_square(o, eps) * (1.0 - diff))
-    o = torch.cat(heads, dim=1) * torch.sigmoid(h @ W[p + "mix.g"].T)
-    return o @ W[p + "mix.o"].T
+    o = torch.cat(heads, dim=1) * torch.sigmoid(product(h, W[p + "mix.g"]))
+    return product(o, W[p + "mix.o"])
 
 
 # ---------------------------------------------------------------- feed-forwards
 def dense_feed_forward(h, W, p):
-    z = squared_relu(h @ W[p + "mlp.up"].T + W[p + "mlp.up.b"])
-    return z @ W[p + "mlp.down"].T + W[p + "mlp.down.b"]
+    z = squared_relu(product(h, W[p + "mlp.up"]) + W[p + "mlp.up.b"])
+    return product(z, W[p + "mlp.down"]) + W[p + "mlp.down.b"]
 
 
 def router_choice(h, W, p, top):
@@ -136,7 +141,7 @@ def mixture_of_experts(h, W, p, mlp, choice=None):
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t].tolist(), weights[t]):
             q = f"{p}mlp.e{e}."
-            out[t] += w * ((silu(h[t] @ W[q + "gate"].T) * (h[t] @ W[q + "up"].T)) @ W[q + "down"].T)
+            out[t] += w * product(silu(product(h[t], W[q + "gate"])) * product(h[t], W[q + "up"]), W[q + "down"])
     return out
 
 
@@ -148,8 +153,8 @@ def feed_forward(h, W, p, mlp):
 def token_side_input(x, tokens, W, p, layer, dim, eps):
     """A few numbers per (token id, layer), gated by the stream, projected to its width and normed."""
     e = W["side.embed"][tokens][:, layer * dim:(layer + 1) * dim]
-    g = gelu_tanh(x @ W[p + "side.gate"].T) * e
-    y = g @ W[p + "side.proj"].T
+    g = gelu_tanh(product(x, W[p + "side.gate"])) * e
+    y = product(g, W[p + "side.proj"])
     return over_root_mean_square(y, eps) * W[p + "side.norm"]
 
 
@@ -170,17 +175,19 @@ def layer(x, tokens, W, config, i):
         y = feed_forward(x, W, p, L["mlp"]) * residual_gate(x, W[p + "rg2"], W[p + "rg2.b"])
         x = x + layer_norm(y, W[p + "norm2"], W[p + "norm2.b"], eps)
     side = config.get("token_side")
-    if side:
+    if side and side.get("dim"):
         x = x + token_side_input(x, tokens, W, p, i, side["dim"], eps)
     return x
 
 
-def forward(config, weights, tokens, return_layers=False):
+def forward(config, weights, tokens, return_layers=False, reads=None):
     """Logits [T, vocab] of one sequence (float64); with ``return_layers`` also every layer's result, before the depth
-    average that follows it."""
+    average that follows it.  ``reads``: a rounding applied to what every product reads and to what it returns (to see
+    how far roundings alone move the result; the router's product is exempt, it is 32-bit in every run)."""
     W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = W["embed"][tokens]
+    _ROUNDING[0] = reads
     results, layers = [x], []
     for i in range(len(config["layers"])):
         X = layer(x, tokens, W, config, i)
@@ -188,5 +195,7 @@ def forward(config, weights, tokens, return_layers=False):
         results.append(X)
         x = depth_average(results, W[f"l{i}.dwa"])
     eps = float(config["norm"]["eps"])
-    logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["embed"].T
+    last = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
+    logits = (reads(last) if reads else last) @ W["embed"].T
+    _ROUNDING[0] = None
     return (logits, layers) if return_layers else logits
