@@ -16,6 +16,7 @@ F = torch.float64
 
 # ---------------------------------------------------------------- small functions
 _ROUNDING = [None]   # a function applied to what every product reads and returns while ``forward(..., reads=f)`` runs
+_MARGINS = [None]    # a list that receives, per routed layer, every token's routing margin while ``forward(..., margins=l)`` runs
 
 
 def product(x, w):
@@ -130,9 +131,25 @@ def dense_feed_forward(h, W, p):
 
 def router_choice(h, W, p, top):
     """Chosen experts [T, top] (largest logits first) and their weights: the softmax over the chosen logits alone."""
-    z = h @ W[p + "mlp.router"].T + W[p + "mlp.router.b"]
+    w = W[p + "mlp.router"]
+    z = h @ w.T + W[p + "mlp.router.b"]
     best, chosen = torch.topk(z, top, dim=-1)
+    if _MARGINS[0] is not None:
+        _MARGINS[0].append(routing_margin(h, w, z, top))
     return chosen, torch.softmax(best, dim=-1)
+
+
+def routing_margin(h, w, z, top):
+    """Per token: how far the last chosen logit lies above the best one left out, as a share of the length of the vector
+    h_i (w_a,i - w_b,i) (independent relative errors of that share in every h_i move the difference of the two logits by
+    about as much as it is).  Infinite when every expert is chosen."""
+    if top >= z.shape[-1]:
+        return torch.full((h.shape[0],), math.inf, dtype=F)
+    order = torch.argsort(z, dim=-1, descending=True)
+    a, b = order[:, top - 1], order[:, top]
+    gap = z.gather(1, a[:, None])[:, 0] - z.gather(1, b[:, None])[:, 0]
+    reach = torch.linalg.vector_norm(h * (w[a] - w[b]), dim=-1)
+    return gap / (reach + 1e-300)
 
 
 def mixture_of_experts(h, W, p, mlp, choice=None):
@@ -180,14 +197,15 @@ def layer(x, tokens, W, config, i):
     return x
 
 
-def forward(config, weights, tokens, return_layers=False, reads=None):
+def forward(config, weights, tokens, return_layers=False, reads=None, margins=None):
     """Logits [T, vocab] of one sequence (float64); with ``return_layers`` also every layer's result, before the depth
     average that follows it.  ``reads``: a rounding applied to what every product reads and to what it returns (to see
-    how far roundings alone move the result; the router's product is exempt, it is 32-bit in every run)."""
+    how far roundings alone move the result; the router's product is exempt, it is 32-bit in every run).  ``margins``: a
+    list that receives one tensor [T] per routed layer, every token's ``routing_margin``."""
     W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = W["embed"][tokens]
-    _ROUNDING[0] = reads
+    _ROUNDING[0], _MARGINS[0] = reads, margins
     results, layers = [x], []
     for i in range(len(config["layers"])):
         X = layer(x, tokens, W, config, i)
@@ -197,5 +215,5 @@ def forward(config, weights, tokens, return_layers=False, reads=None):
     eps = float(config["norm"]["eps"])
     last = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
     logits = (reads(last) if reads else last) @ W["embed"].T
-    _ROUNDING[0] = None
+    _ROUNDING[0] = _MARGINS[0] = None
     return (logits, layers) if return_layers else logits
