@@ -10,6 +10,11 @@
 //   cast_rows          xc = x in the run's type (what a product over the stream itself reads)
 //   bias_act_rows      u <- act(u + bias) in place on a product's result; act: the square of max(., 0)
 //   token_gate_rows    g[t, j] = gelu_tanh(a[t, j]) * table[token[t], j]: a few numbers per token id that the stream gates
+//   token_side_step    steps of few tokens: the whole token input and what follows it in one kernel, a CTA per token:
+//                      a = W_s x ;  g = gelu_tanh(a) * table[token] ;  y = W_p g ;  x <- x + w * y / rms(y) ;  then the
+//                      mix over the levels as depth_average does it, and xc; a and g are rounded to the run's type where
+//                      the separate kernels round them, so that a token's result does not depend on the step's size
+//                      beyond the order of two short sums
 //
 // A CTA per token row for the three steps: a thread keeps its share of the row (the elements tid, tid + 256, ...) in
 // registers between the one fetch and the one store when the row has at most 256 * 32 numbers; longer rows are
@@ -103,7 +108,111 @@ gated_norm_step_kernel(GatedNormArgs a) {
     }
 }
 
-// level[n] = x ; x <- sum_j c[j] level[j] (j = 0 .. n, in that order) ; xc = x.  Elementwise: a thread per four numbers.
+// Four numbers of type T as floats, and back (16-byte or 8-byte accesses; the caller checks the alignment).
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = w;
+}
+
+// The same step for rows of whole groups of four numbers (dim <= 4 NV kStepThreads): a thread keeps NV groups of four in
+// registers and moves them with 16-byte accesses, all of a row's fetches in flight together.
+template <typename TR, typename TC, int NV>
+__global__ void __launch_bounds__(kStepThreads)
+gated_norm_step_vec_kernel(GatedNormArgs a) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x, dim = a.dim;
+    float* yr = a.y + (size_t)t * dim;
+    float* xr = a.x + (size_t)t * dim;
+    const TR* rr = a.r ? (const TR*)a.r + (size_t)t * a.ld_r : nullptr;
+    float4 z[NV], xv[NV];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = (tid + j * kStepThreads) * 4;
+        z[j] = xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < dim) {
+            z[j] = load4<float>(yr + i);
+            xv[j] = load4<float>(xr + i);
+            if (a.y_bias) {
+                const float4 b = load4<float>(a.y_bias + i);
+                z[j].x += b.x; z[j].y += b.y; z[j].z += b.z; z[j].w += b.w;
+            }
+            if (rr) {
+                float4 r = load4<TR>(rr + i);
+                if (a.r_bias) {
+                    const float4 b = load4<float>(a.r_bias + i);
+                    r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+                }
+                z[j].x *= sigmoid_f(r.x); z[j].y *= sigmoid_f(r.y); z[j].z *= sigmoid_f(r.z); z[j].w *= sigmoid_f(r.w);
+            }
+            sum += (z[j].x + z[j].y) + (z[j].z + z[j].w);
+        }
+    }
+    float mean = 0.f;
+    if (a.center) mean = block_sum(sum, scratch) / (float)dim;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = (tid + j * kStepThreads) * 4;
+        if (i < dim) {
+            const float d0 = z[j].x - mean, d1 = z[j].y - mean, d2 = z[j].z - mean, d3 = z[j].w - mean;
+            ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
+    TC* xc = a.xc ? (TC*)a.xc + (size_t)t * dim : nullptr;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = (tid + j * kStepThreads) * 4;
+        if (i >= dim) continue;
+        const float4 w = load4<float>(a.w + i);
+        const float4 b = a.b ? load4<float>(a.b + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v;
+        v.x = xv[j].x + ((z[j].x - mean) * scale * w.x + b.x);
+        v.y = xv[j].y + ((z[j].y - mean) * scale * w.y + b.y);
+        v.z = xv[j].z + ((z[j].z - mean) * scale * w.z + b.z);
+        v.w = xv[j].w + ((z[j].w - mean) * scale * w.w + b.w);
+        store4<float>(xr + i, v);
+        store4<float>(yr + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        if (xc) store4<TC>(xc + i, v);
+    }
+}
+
+// level[n] = x ; x <- sum_j c[j] level[j] (j = 0 .. n, in that order) ; xc = x.  Elementwise: a thread per four numbers
+// where the rows allow 16-byte accesses (depth_average_vec_kernel), else per number.
+template <typename TR>
+__global__ void __launch_bounds__(256)
+depth_average_vec_kernel(float* __restrict__ levels, size_t level_stride, int n, const float* __restrict__ c,
+                         float* __restrict__ x, TR* __restrict__ xc, size_t total4) {
+    for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = q * 4;
+        const float4 newest = load4<float>(x + i);
+        store4<float>(levels + (size_t)n * level_stride + i, newest);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n; ++j) {
+            const float4 v = load4<float>(levels + (size_t)j * level_stride + i);
+            const float cj = c[j];
+            acc.x += cj * v.x; acc.y += cj * v.y; acc.z += cj * v.z; acc.w += cj * v.w;
+        }
+        const float cn = c[n];
+        acc.x += cn * newest.x; acc.y += cn * newest.y; acc.z += cn * newest.z; acc.w += cn * newest.w;
+        store4<float>(x + i, acc);
+        if (xc) store4<TR>(xc + i, acc);
+    }
+}
+
 template <typename TR>
 __global__ void __launch_bounds__(256)
 depth_average_kernel(float* __restrict__ levels, size_t level_stride, int n, const float* __restrict__ c,
@@ -149,8 +258,112 @@ token_gate_rows_kernel(const TR* __restrict__ a, int ld_a, const int* __restrict
         g[(size_t)t * ld_g + j] = from_f32<TR>(j < n ? gelu_tanh_f(to_f32<TR>(a[(size_t)t * ld_a + j])) * to_f32<TT>(e[j]) : 0.f);
 }
 
+struct SideStepArgs {
+    float* x;                 // [T][dim]
+    const int* tokens;        // [T]
+    const void* table;        // [n_rows_table][ld_table], first `sdim` columns
+    int ld_table, n_rows_table;
+    const void* w_gate;       // [>= sdim][dim], the run's type
+    const void* w_proj;       // [dim][side_k], the run's type (columns beyond sdim are zero)
+    const float* w_norm;      // [dim]
+    float eps;
+    int dim, sdim, side_k;
+    float* levels;            // [> n][level_stride] or null: no mix over the levels
+    size_t level_stride;
+    int n;
+    const float* c;           // [n + 1]
+    void* xc;                 // [T][dim] in the run's type, or null
+};
+
+// dim <= NV * kStepThreads, sdim <= kMaxSide.  Shared: dim + sdim floats.
+constexpr int kMaxSide = 1024;
+template <typename T, typename TT, int NV>
+__global__ void __launch_bounds__(kStepThreads)
+token_side_step_kernel(SideStepArgs a) {
+    extern __shared__ float side_shared[];
+    __shared__ float scratch[33];
+    float* xs = side_shared;            // the stream's row as the products read it (rounded to the run's type)
+    float* g = xs + a.dim;              // the gated numbers
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, dim = a.dim;
+    float* xr = a.x + (size_t)t * dim;
+    for (int i = tid; i < dim; i += kStepThreads) xs[i] = to_f32<T>(from_f32<T>(xr[i]));
+    __syncthreads();
+    int tok = a.tokens[t];
+    tok = tok < 0 ? 0 : (tok >= a.n_rows_table ? a.n_rows_table - 1 : tok);
+    const TT* e = (const TT*)a.table + (size_t)tok * a.ld_table;
+    for (int j = warp; j < a.sdim; j += kStepThreads / 32) {
+        const T* w = (const T*)a.w_gate + (size_t)j * dim;
+        float acc = 0.f;
+        for (int k = lane; k < dim; k += 32) acc += to_f32<T>(w[k]) * xs[k];
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float pre = to_f32<T>(from_f32<T>(acc));
+            g[j] = to_f32<T>(from_f32<T>(gelu_tanh_f(pre) * to_f32<TT>(e[j])));
+        }
+    }
+    __syncthreads();
+    float y[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = tid + v * kStepThreads;
+        float acc = 0.f;
+        if (i < dim) {
+            const T* w = (const T*)a.w_proj + (size_t)i * a.side_k;
+            for (int j = 0; j < a.sdim; ++j) acc += to_f32<T>(w[j]) * g[j];
+        }
+        y[v] = acc;
+        ss += acc * acc;
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
+    T* xc = a.xc ? (T*)a.xc + (size_t)t * dim : nullptr;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = tid + v * kStepThreads;
+        if (i >= dim) continue;
+        float value = xr[i] + y[v] * scale * a.w_norm[i];
+        if (a.levels) {
+            const size_t at = (size_t)t * dim + i;
+            a.levels[(size_t)a.n * a.level_stride + at] = value;
+            float acc = 0.f;
+            for (int j = 0; j < a.n; ++j) acc += a.c[j] * a.levels[(size_t)j * a.level_stride + at];
+            value = acc + a.c[a.n] * value;
+        }
+        xr[i] = value;
+        if (xc) xc[i] = from_f32<T>(value);
+    }
+}
+
+template <typename T, typename TT>
+static int launch_token_side_step(const SideStepArgs& a, int n_tokens, cudaStream_t stream) {
+    const int per = (a.dim + kStepThreads - 1) / kStepThreads;
+    const size_t smem = sizeof(float) * ((size_t)a.dim + a.sdim);
+#define B200_SIDE_STEP_CASE(NV) token_side_step_kernel<T, TT, NV><<<n_tokens, kStepThreads, smem, stream>>>(a)
+    if (per <= 1) B200_SIDE_STEP_CASE(1);
+    else if (per <= 2) B200_SIDE_STEP_CASE(2);
+    else if (per <= 4) B200_SIDE_STEP_CASE(4);
+    else if (per <= 8) B200_SIDE_STEP_CASE(8);
+    else if (per <= 16) B200_SIDE_STEP_CASE(16);
+    else return kErrUnsupportedSize;
+#undef B200_SIDE_STEP_CASE
+    return launch_status();
+}
+
 template <typename TR, typename TC>
 static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t stream) {
+    // rows of whole groups of four whose every pointer lies on a 16-byte boundary (8 bytes for 16-bit rows) go four at a time
+    const uintptr_t all = (uintptr_t)a.y | (uintptr_t)a.x | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y_bias |
+                          (uintptr_t)a.r_bias | (uintptr_t)a.r | (uintptr_t)a.xc;
+    if (a.dim % 4 == 0 && a.ld_r % 4 == 0 && (all & 15) == 0 && a.dim <= 32 * kStepThreads) {
+        const int per4 = (a.dim / 4 + kStepThreads - 1) / kStepThreads;
+#define B200_GATED_NORM_VEC(NV) gated_norm_step_vec_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
+        if (per4 <= 1) B200_GATED_NORM_VEC(1);
+        else if (per4 <= 2) B200_GATED_NORM_VEC(2);
+        else if (per4 <= 4) B200_GATED_NORM_VEC(4);
+        else B200_GATED_NORM_VEC(8);
+#undef B200_GATED_NORM_VEC
+        return launch_status();
+    }
     const int per = (a.dim + kStepThreads - 1) / kStepThreads;
 #define B200_GATED_NORM_CASE(NV) gated_norm_step_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
     if (per <= 1) B200_GATED_NORM_CASE(1);
@@ -183,6 +396,14 @@ extern "C" int b200_depth_average(float* levels, long long level_stride, int n, 
                                   long long total, cudaStream_t stream) {
     if (total <= 0) return 0;
     if (n < 0 || !levels || !c || !x || level_stride < total) return b200::kErrBadArgument;
+    if (total % 4 == 0 && level_stride % 4 == 0 && (((uintptr_t)levels | (uintptr_t)x | (uintptr_t)xc) & 15) == 0) {
+        const long long blocks4 = (total / 4 + 255) / 256;
+        const int grid4 = (int)(blocks4 < 148 * 16 ? blocks4 : 148 * 16);
+        B200_DISPATCH_DTYPE(dtype, T,
+            b200::depth_average_vec_kernel<T><<<grid4, 256, 0, stream>>>(levels, (size_t)level_stride, n, c, x, (T*)xc,
+                                                                       (size_t)(total / 4)));
+        return b200::launch_status();
+    }
     const long long blocks = (total + 255) / 256;
     const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
     B200_DISPATCH_DTYPE(dtype, T,
@@ -219,4 +440,21 @@ extern "C" int b200_token_gate_rows(const void* a, int ld_a, int dtype, const in
             b200::token_gate_rows_kernel<T, TT><<<n_tokens, 128, 0, stream>>>((const T*)a, ld_a, tokens, (const TT*)table, ld_table,
                                                                              n_rows_table, (T*)g, ld_g, n, width)));
     return b200::launch_status();
+}
+
+// A step of few tokens: the token input, its norm into the stream and (levels not null) the mix over the levels.
+// dim <= 4096 and sdim <= 1024; other sizes are refused (the caller then runs the separate kernels).
+extern "C" int b200_token_side_step(float* x, const int* tokens, const void* table, int table_dtype, int ld_table,
+                                    int n_rows_table, const void* w_gate, const void* w_proj, int dtype, const float* w_norm,
+                                    float eps, int n_tokens, int dim, int sdim, int side_k, float* levels,
+                                    long long level_stride, int n, const float* c, void* xc, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!x || !tokens || !table || !w_gate || !w_proj || !w_norm || dim < 1 || sdim < 1 || side_k < sdim || n_rows_table < 1)
+        return b200::kErrBadArgument;
+    if (levels && (n < 0 || !c || level_stride < (long long)n_tokens * dim)) return b200::kErrBadArgument;
+    if (dim > 16 * b200::kStepThreads || sdim > b200::kMaxSide) return b200::kErrUnsupportedSize;
+    const b200::SideStepArgs a = {x, tokens, table, ld_table, n_rows_table, w_gate, w_proj, w_norm, eps, dim, sdim, side_k,
+                                  levels, (size_t)level_stride, n, c, xc};
+    B200_DISPATCH_DTYPE(dtype, T, B200_DISPATCH_DTYPE2(table_dtype, TT, return b200::launch_token_side_step<T, TT>(a, n_tokens, stream)));
+    return 0;
 }

@@ -15,7 +15,8 @@ of what a run of the block keeps per sequence (32-bit, beside the mixer's cache)
 the block is built with (layer norms with weight and bias, or RMS norms); the gates read the sublayer's own input before
 the convolution.  A sublayer's last product adds into a 32-bit row buffer of the pass; one kernel then gates and norms
 that result into the stream, clears the buffer and leaves the updated stream in the run's type for the products that
-read it next (the gate's, the feed-forward's, the next block's).  The stream, the gates' logits and sigmoid, the norms,
+read it next (the gate's, the feed-forward's, the next block's).  In a step in which every sequence brings one token
+the token input, its norm and the mix over the levels are one kernel (a CTA per token).  The stream, the gates' logits and sigmoid, the norms,
 the convolution with its state and the mix over the levels are 32-bit in both precisions."""
 from __future__ import annotations
 
@@ -186,6 +187,16 @@ class GatedResidualBlock(Block):
             else:
                 self.feed_forward.forward(x, ctx, y)
             x = self._join(y, x, 1, self.feed_forward_norm, residual, ctx, y_bias=y_bias, cast=cast_behind("feed_forward"))
+        if self.side_dim and ctx.all_decode and ops.token_side_step_fits(h, self.side_dim):
+            # a step of one token per sequence: the token input, its norm and the mix over the levels in one kernel
+            run = self.side_gate.weight.dtype
+            ops.token_side_step(residual, ctx.tokens, self.side_table, self.side_gate.weight, self.side_proj.weight, self.side_norm,
+                                self.side_eps, self.side_dim, levels=levels, n=self.depth[0] + 1 if self.depth is not None else 0,
+                                coefficients=self.depth_mix if self.depth is not None else None,
+                                cast=last if last.dtype == run else None)
+            if last.dtype != run:
+                ops.cast_rows(residual, last)
+            return StreamRows(last)
         if self.side_dim:
             a = self.side_gate.store(x, ctx.dtype, ctx.empty)
             g = ctx.empty((T, self.side_k), ctx.dtype)

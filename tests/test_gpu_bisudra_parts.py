@@ -35,12 +35,14 @@ def _ctx(cache, dtype, slots, token_lists):
 @DTYPES
 @pytest.mark.parametrize("rows, dim", [(5, 48), (3, 640), (300, 1024), (2, 8192), (2, 8448), (7, 1), (4, 257)])
 @pytest.mark.parametrize("gated, centred, result_bias", [(True, True, True), (True, True, False), (False, False, False), (True, False, True)])
-def test_gated_norm_into_the_stream(dtype, rows, dim, gated, centred, result_bias):
+@pytest.mark.parametrize("pad, gate_type", [(3, None), (4, None), (8, torch.float32)], ids=["ragged", "whole fours", "32-bit gate"])
+def test_gated_norm_into_the_stream(dtype, rows, dim, gated, centred, result_bias, pad, gate_type):
+    """``pad``: further columns of the gate's rows (rows of whole fours go four numbers at a time)."""
     from gpullama3.java_b200.kernels import ops
 
     g = torch.Generator().manual_seed(rows * dim + gated)
     x, y = torch.randn(rows, dim, generator=g) * 4, torch.randn(rows, dim, generator=g) * 0.01 + 0.02
-    r = (torch.randn(rows, dim + 3, generator=g) * 2).to(dtype)
+    r = (torch.randn(rows, dim + pad, generator=g) * 2).to(gate_type or dtype)
     w, b, rb, yb = (torch.randn(dim, generator=g) for _ in range(4))
     yb = yb * 0.01
     xd, yd = x.to(DEV), y.to(DEV)
