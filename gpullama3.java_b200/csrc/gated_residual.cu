@@ -4,17 +4,13 @@
 //   gated_norm_step    z = (y (+ yb)) * sigmoid(r + rb)                  the sublayer's result y times its gate, whose
 //                      x <- x + (z - mean(z)) / sqrt(var(z) + eps) * w + b    logits r come from a product over the
 //                      y <- 0 ;  xc = x in the run's type (optional)      sublayer's own input; a layer norm; the sum
-//   rms_add_step       x <- x + y / sqrt(mean(y^2) + eps) * w ;  y <- 0 ;  xc = x (optional)
+//                      the same without a gate and without the mean: x <- x + w * y / sqrt(mean(y^2) + eps)
+//                      and, for the last such step of a layer whose results are mixed, depth_average in the same pass
 //   depth_average      level[n] = x ;  x <- sum_(j <= n) c[j] level[j] ;  xc = x (optional): every layer's result is
 //                      kept for the pass, and what the next layer reads is a learned mix of all of them
 //   cast_rows          xc = x in the run's type (what a product over the stream itself reads)
 //   bias_act_rows      u <- act(u + bias) in place on a product's result; act: the square of max(., 0)
 //   token_gate_rows    g[t, j] = gelu_tanh(a[t, j]) * table[token[t], j]: a few numbers per token id that the stream gates
-//   token_side_step    steps of few tokens: the whole token input and what follows it in one kernel, a CTA per token:
-//                      a = W_s x ;  g = gelu_tanh(a) * table[token] ;  y = W_p g ;  x <- x + w * y / rms(y) ;  then the
-//                      mix over the levels as depth_average does it, and xc; a and g are rounded to the run's type where
-//                      the separate kernels round them, so that a token's result does not depend on the step's size
-//                      beyond the order of two short sums
 //
 // A CTA per token row for the three steps: a thread keeps its share of the row (the elements tid, tid + 256, ...) in
 // registers between the one fetch and the one store when the row has at most 256 * 32 numbers; longer rows are
@@ -44,7 +40,19 @@ struct GatedNormArgs {
     int dim;
     float eps;
     int center;             // 1: layer norm; 0: divide by the root mean square only
+    float* levels;          // [> n][level_stride] or null; not null: the new x is filed as level n and what is left as
+    size_t level_stride;    // the stream (and in xc) is sum_(j <= n) c[j] level[j], as depth_average does it
+    int n;
+    const float* c;         // [n + 1]
 };
+
+// The mix over the levels for one number: files `value` as level n, returns sum_j c[j] level[j] (j in order).
+__device__ __forceinline__ float mix_levels(const GatedNormArgs& a, size_t at, float value) {
+    a.levels[(size_t)a.n * a.level_stride + at] = value;
+    float acc = 0.f;
+    for (int j = 0; j < a.n; ++j) acc += a.c[j] * a.levels[(size_t)j * a.level_stride + at];
+    return acc + a.c[a.n] * value;
+}
 
 // NV > 0: the row's values stay in registers (dim <= NV * kStepThreads); NV == 0: any size, evaluated per pass.
 template <typename TR, typename TC, int NV>
@@ -92,7 +100,8 @@ gated_norm_step_kernel(GatedNormArgs a) {
     const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
     TC* xc = a.xc ? (TC*)a.xc + (size_t)t * dim : nullptr;
     auto finish = [&](int i, float z) {
-        const float v = xr[i] + ((z - mean) * scale * a.w[i] + (a.b ? a.b[i] : 0.f));
+        float v = xr[i] + ((z - mean) * scale * a.w[i] + (a.b ? a.b[i] : 0.f));
+        if (a.levels) v = mix_levels(a, (size_t)t * dim + i, v);
         xr[i] = v;
         yr[i] = 0.f;
         if (xc) xc[i] = from_f32<TC>(v);
@@ -184,6 +193,18 @@ gated_norm_step_vec_kernel(GatedNormArgs a) {
         v.y = xv[j].y + ((z[j].y - mean) * scale * w.y + b.y);
         v.z = xv[j].z + ((z[j].z - mean) * scale * w.z + b.z);
         v.w = xv[j].w + ((z[j].w - mean) * scale * w.w + b.w);
+        if (a.levels) {
+            const size_t at = (size_t)t * dim + i;
+            store4<float>(a.levels + (size_t)a.n * a.level_stride + at, v);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < a.n; ++k) {
+                const float4 l = load4<float>(a.levels + (size_t)k * a.level_stride + at);
+                const float ck = a.c[k];
+                acc.x += ck * l.x; acc.y += ck * l.y; acc.z += ck * l.z; acc.w += ck * l.w;
+            }
+            const float cn = a.c[a.n];
+            v = make_float4(acc.x + cn * v.x, acc.y + cn * v.y, acc.z + cn * v.z, acc.w + cn * v.w);
+        }
         store4<float>(xr + i, v);
         store4<float>(yr + i, make_float4(0.f, 0.f, 0.f, 0.f));
         if (xc) store4<TC>(xc + i, v);
@@ -258,103 +279,12 @@ token_gate_rows_kernel(const TR* __restrict__ a, int ld_a, const int* __restrict
         g[(size_t)t * ld_g + j] = from_f32<TR>(j < n ? gelu_tanh_f(to_f32<TR>(a[(size_t)t * ld_a + j])) * to_f32<TT>(e[j]) : 0.f);
 }
 
-struct SideStepArgs {
-    float* x;                 // [T][dim]
-    const int* tokens;        // [T]
-    const void* table;        // [n_rows_table][ld_table], first `sdim` columns
-    int ld_table, n_rows_table;
-    const void* w_gate;       // [>= sdim][dim], the run's type
-    const void* w_proj;       // [dim][side_k], the run's type (columns beyond sdim are zero)
-    const float* w_norm;      // [dim]
-    float eps;
-    int dim, sdim, side_k;
-    float* levels;            // [> n][level_stride] or null: no mix over the levels
-    size_t level_stride;
-    int n;
-    const float* c;           // [n + 1]
-    void* xc;                 // [T][dim] in the run's type, or null
-};
-
-// dim <= NV * kStepThreads, sdim <= kMaxSide.  Shared: dim + sdim floats.
-constexpr int kMaxSide = 1024;
-template <typename T, typename TT, int NV>
-__global__ void __launch_bounds__(kStepThreads)
-token_side_step_kernel(SideStepArgs a) {
-    extern __shared__ float side_shared[];
-    __shared__ float scratch[33];
-    float* xs = side_shared;            // the stream's row as the products read it (rounded to the run's type)
-    float* g = xs + a.dim;              // the gated numbers
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, dim = a.dim;
-    float* xr = a.x + (size_t)t * dim;
-    for (int i = tid; i < dim; i += kStepThreads) xs[i] = to_f32<T>(from_f32<T>(xr[i]));
-    __syncthreads();
-    int tok = a.tokens[t];
-    tok = tok < 0 ? 0 : (tok >= a.n_rows_table ? a.n_rows_table - 1 : tok);
-    const TT* e = (const TT*)a.table + (size_t)tok * a.ld_table;
-    for (int j = warp; j < a.sdim; j += kStepThreads / 32) {
-        const T* w = (const T*)a.w_gate + (size_t)j * dim;
-        float acc = 0.f;
-        for (int k = lane; k < dim; k += 32) acc += to_f32<T>(w[k]) * xs[k];
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float pre = to_f32<T>(from_f32<T>(acc));
-            g[j] = to_f32<T>(from_f32<T>(gelu_tanh_f(pre) * to_f32<TT>(e[j])));
-        }
-    }
-    __syncthreads();
-    float y[NV];
-    float ss = 0.f;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-        const int i = tid + v * kStepThreads;
-        float acc = 0.f;
-        if (i < dim) {
-            const T* w = (const T*)a.w_proj + (size_t)i * a.side_k;
-            for (int j = 0; j < a.sdim; ++j) acc += to_f32<T>(w[j]) * g[j];
-        }
-        y[v] = acc;
-        ss += acc * acc;
-    }
-    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + a.eps);
-    T* xc = a.xc ? (T*)a.xc + (size_t)t * dim : nullptr;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-        const int i = tid + v * kStepThreads;
-        if (i >= dim) continue;
-        float value = xr[i] + y[v] * scale * a.w_norm[i];
-        if (a.levels) {
-            const size_t at = (size_t)t * dim + i;
-            a.levels[(size_t)a.n * a.level_stride + at] = value;
-            float acc = 0.f;
-            for (int j = 0; j < a.n; ++j) acc += a.c[j] * a.levels[(size_t)j * a.level_stride + at];
-            value = acc + a.c[a.n] * value;
-        }
-        xr[i] = value;
-        if (xc) xc[i] = from_f32<T>(value);
-    }
-}
-
-template <typename T, typename TT>
-static int launch_token_side_step(const SideStepArgs& a, int n_tokens, cudaStream_t stream) {
-    const int per = (a.dim + kStepThreads - 1) / kStepThreads;
-    const size_t smem = sizeof(float) * ((size_t)a.dim + a.sdim);
-#define B200_SIDE_STEP_CASE(NV) token_side_step_kernel<T, TT, NV><<<n_tokens, kStepThreads, smem, stream>>>(a)
-    if (per <= 1) B200_SIDE_STEP_CASE(1);
-    else if (per <= 2) B200_SIDE_STEP_CASE(2);
-    else if (per <= 4) B200_SIDE_STEP_CASE(4);
-    else if (per <= 8) B200_SIDE_STEP_CASE(8);
-    else if (per <= 16) B200_SIDE_STEP_CASE(16);
-    else return kErrUnsupportedSize;
-#undef B200_SIDE_STEP_CASE
-    return launch_status();
-}
-
 template <typename TR, typename TC>
 static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t stream) {
     // rows of whole groups of four whose every pointer lies on a 16-byte boundary (8 bytes for 16-bit rows) go four at a time
     const uintptr_t all = (uintptr_t)a.y | (uintptr_t)a.x | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y_bias |
-                          (uintptr_t)a.r_bias | (uintptr_t)a.r | (uintptr_t)a.xc;
-    if (a.dim % 4 == 0 && a.ld_r % 4 == 0 && (all & 15) == 0 && a.dim <= 32 * kStepThreads) {
+                          (uintptr_t)a.r_bias | (uintptr_t)a.r | (uintptr_t)a.xc | (uintptr_t)a.levels;
+    if (a.dim % 4 == 0 && a.ld_r % 4 == 0 && (all & 15) == 0 && a.level_stride % 4 == 0 && a.dim <= 32 * kStepThreads) {
         const int per4 = (a.dim / 4 + kStepThreads - 1) / kStepThreads;
 #define B200_GATED_NORM_VEC(NV) gated_norm_step_vec_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
         if (per4 <= 1) B200_GATED_NORM_VEC(1);
@@ -380,13 +310,17 @@ static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t 
 }  // namespace b200
 
 // `center` 1: x += layer norm of the gated result (w, b); 0: x += w * z / rms(z) (b ignored).  `r` null: no gate.
-// `r_dtype`: the gate logits' type; `dtype`: that of xc.
+// `r_dtype`: the gate logits' type; `dtype`: that of xc.  `levels` not null: the new x is filed as level `n` of
+// levels [> n][level_stride] and the stream becomes sum_(j <= n) c[j] level[j] (c on the device), as b200_depth_average does it.
 extern "C" int b200_gated_norm_step(float* y, const float* y_bias, const void* r, int ld_r, int r_dtype, const float* r_bias,
                                     const float* w, const float* b, float* x, void* xc, int dtype, int n_tokens, int dim,
-                                    float eps, int center, cudaStream_t stream) {
+                                    float eps, int center, float* levels, long long level_stride, int n, const float* c,
+                                    cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dim < 1 || !y || !w || !x || (r && ld_r < dim)) return b200::kErrBadArgument;
-    const b200::GatedNormArgs a = {y, y_bias, r, ld_r, r_bias, w, center ? b : nullptr, x, xc, dim, eps, center ? 1 : 0};
+    if (levels && (n < 0 || !c || level_stride < (long long)n_tokens * dim)) return b200::kErrBadArgument;
+    const b200::GatedNormArgs a = {y, y_bias, r, ld_r, r_bias, w, center ? b : nullptr, x, xc, dim, eps, center ? 1 : 0,
+                                   levels, (size_t)(levels ? level_stride : 0), n, c};
     B200_DISPATCH_DTYPE(r_dtype, TR, B200_DISPATCH_DTYPE2(dtype, TC, return b200::launch_gated_norm<TR, TC>(a, n_tokens, stream)));
     return 0;
 }
@@ -442,19 +376,3 @@ extern "C" int b200_token_gate_rows(const void* a, int ld_a, int dtype, const in
     return b200::launch_status();
 }
 
-// A step of few tokens: the token input, its norm into the stream and (levels not null) the mix over the levels.
-// dim <= 4096 and sdim <= 1024; other sizes are refused (the caller then runs the separate kernels).
-extern "C" int b200_token_side_step(float* x, const int* tokens, const void* table, int table_dtype, int ld_table,
-                                    int n_rows_table, const void* w_gate, const void* w_proj, int dtype, const float* w_norm,
-                                    float eps, int n_tokens, int dim, int sdim, int side_k, float* levels,
-                                    long long level_stride, int n, const float* c, void* xc, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (!x || !tokens || !table || !w_gate || !w_proj || !w_norm || dim < 1 || sdim < 1 || side_k < sdim || n_rows_table < 1)
-        return b200::kErrBadArgument;
-    if (levels && (n < 0 || !c || level_stride < (long long)n_tokens * dim)) return b200::kErrBadArgument;
-    if (dim > 16 * b200::kStepThreads || sdim > b200::kMaxSide) return b200::kErrUnsupportedSize;
-    const b200::SideStepArgs a = {x, tokens, table, ld_table, n_rows_table, w_gate, w_proj, w_norm, eps, dim, sdim, side_k,
-                                  levels, (size_t)level_stride, n, c, xc};
-    B200_DISPATCH_DTYPE(dtype, T, B200_DISPATCH_DTYPE2(table_dtype, TT, return b200::launch_token_side_step<T, TT>(a, n_tokens, stream)));
-    return 0;
-}

@@ -120,16 +120,14 @@ _SIGNATURES = {
     "b200_differential_heads": ("elementwise", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                                 c_float, c_float]),
     "b200_gated_norm_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                c_void_p, c_int, c_int, c_int, c_float, c_int]),
+                                                c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, ctypes.c_longlong, c_int,
+                                                c_void_p]),
     "b200_depth_average": ("gated_residual", [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               ctypes.c_longlong]),
     "b200_cast_rows": ("gated_residual", [c_void_p, c_void_p, c_int, ctypes.c_longlong]),
     "b200_bias_act_rows": ("gated_residual", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int]),
     "b200_token_gate_rows": ("gated_residual", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                                                 c_int, c_int, c_int]),
-    "b200_token_side_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                                                c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, ctypes.c_longlong, c_int,
-                                                c_void_p, c_void_p]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -975,10 +973,12 @@ def differential_heads(maps: torch.Tensor, gate: torch.Tensor | None, out: torch
 # --------------------------------------------------------------------------- a block that gates and norms what its sublayers return
 def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, x: torch.Tensor, eps: float, *,
                     gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None,
-                    y_bias: torch.Tensor | None = None, cast: torch.Tensor | None = None, center: bool = True) -> None:
+                    y_bias: torch.Tensor | None = None, cast: torch.Tensor | None = None, center: bool = True,
+                    levels: torch.Tensor | None = None, n: int = 0, coefficients: torch.Tensor | None = None) -> None:
     """z = (y (+ y_bias)) * sigmoid(gate (+ gate_bias)); x <- x + layer_norm(z) * weight + bias (``center`` False: x <- x +
     weight * z / rms(z)); y <- 0; ``cast`` receives the new x in its own type.  x, y [T, dim], the vectors float32;
-    ``gate`` [T, >= dim], float32 or bfloat16 (None: no gate)."""
+    ``gate`` [T, >= dim], float32 or bfloat16 (None: no gate).  With ``levels`` (float32 [> n, T, dim]) the new x is filed as
+    level ``n`` and what stays as the stream (and in ``cast``) is sum_(j <= n) coefficients[j] levels[j], as ``depth_average``."""
     _dev(y, weight, bias, x, gate, gate_bias, y_bias, cast)
     T, dim = x.shape
     assert x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
@@ -986,11 +986,17 @@ def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == dim)
     assert gate is None or (gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= dim)
     assert cast is None or (cast.is_contiguous() and cast.shape == x.shape)
+    if levels is not None:
+        _dev(levels, coefficients)
+        assert levels.dtype == coefficients.dtype == torch.float32 and levels.is_contiguous() and coefficients.is_contiguous()
+        assert levels.shape[0] > n >= 0 and tuple(levels.shape[1:]) == (T, dim) and coefficients.numel() == n + 1
     ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_gated_norm_step")(y.data_ptr(), ptr(y_bias), ptr(gate), gate.stride(0) if gate is not None else 0,
                                        dtype_code(gate.dtype) if gate is not None else F32, ptr(gate_bias), weight.data_ptr(),
                                        ptr(bias), x.data_ptr(), ptr(cast), dtype_code(cast.dtype) if cast is not None else F32,
-                                       T, dim, float(eps), 1 if center else 0, _stream()), "gated_norm_step")
+                                       T, dim, float(eps), 1 if center else 0, ptr(levels),
+                                       levels.stride(0) if levels is not None else 0, int(n), ptr(coefficients), _stream()),
+           "gated_norm_step")
 
 
 def depth_average(levels: torch.Tensor, n: int, coefficients: torch.Tensor, x: torch.Tensor,
@@ -1033,35 +1039,6 @@ def token_gate_rows(a: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, 
     _check(_fn("b200_token_gate_rows")(a.data_ptr(), a.stride(0), dtype_code(a.dtype), tokens.data_ptr(), table.data_ptr(),
                                        dtype_code(table.dtype), table.stride(0), table.shape[0], out.data_ptr(), out.stride(0),
                                        a.shape[0], int(n), out.shape[1], _stream()), "token_gate_rows")
-
-
-def token_side_step_fits(dim: int, side_dim: int) -> bool:
-    """Whether ``token_side_step`` takes a stream of ``dim`` numbers and ``side_dim`` numbers per token (gated_residual.cu)."""
-    return 1 <= dim <= 4096 and 1 <= side_dim <= 1024
-
-
-def token_side_step(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor, w_proj: torch.Tensor,
-                    w_norm: torch.Tensor, eps: float, side_dim: int, *, levels: torch.Tensor | None = None, n: int = 0,
-                    coefficients: torch.Tensor | None = None, cast: torch.Tensor | None = None) -> None:
-    """A step of few tokens, one kernel: a = w_gate x; g = gelu_tanh(a) * table[token]; y = w_proj g; x <- x + w_norm * y /
-    rms(y); then, with ``levels``, the mix of ``depth_average``; ``cast`` receives the new x in the run's type.
-    w_gate [>= side_dim, dim] and w_proj [dim, >= side_dim] in the run's type (= cast's), table [vocab, >= side_dim]."""
-    _dev(x, tokens, table, w_gate, w_proj, w_norm, levels, coefficients, cast)
-    T, dim = x.shape
-    assert x.dtype == w_norm.dtype == torch.float32 and x.is_contiguous() and w_norm.is_contiguous() and w_norm.numel() == dim
-    assert tokens.dtype == torch.int32 and tokens.numel() == T and table.stride(1) == 1 and table.shape[1] >= side_dim
-    assert w_gate.dtype == w_proj.dtype and w_gate.is_contiguous() and w_proj.is_contiguous()
-    assert w_gate.shape[0] >= side_dim and w_gate.shape[1] == dim and w_proj.shape[0] == dim and w_proj.shape[1] >= side_dim
-    assert cast is None or (cast.dtype == w_gate.dtype and cast.is_contiguous() and cast.shape == x.shape)
-    if levels is not None:
-        assert levels.dtype == coefficients.dtype == torch.float32 and levels.is_contiguous() and coefficients.is_contiguous()
-        assert levels.shape[0] > n >= 0 and tuple(levels.shape[1:]) == (T, dim) and coefficients.numel() == n + 1
-    ptr = lambda t: t.data_ptr() if t is not None else None
-    _check(_fn("b200_token_side_step")(x.data_ptr(), tokens.data_ptr(), table.data_ptr(), dtype_code(table.dtype), table.stride(0),
-                                       table.shape[0], w_gate.data_ptr(), w_proj.data_ptr(), dtype_code(w_gate.dtype),
-                                       w_norm.data_ptr(), float(eps), T, dim, int(side_dim), w_proj.shape[1], ptr(levels),
-                                       levels.stride(0) if levels is not None else 0, int(n), ptr(coefficients), ptr(cast),
-                                       _stream()), "token_side_step")
 
 
 # --------------------------------------------------------------------------- norms in groups, and a block that norms both ways

@@ -15,8 +15,8 @@ of what a run of the block keeps per sequence (32-bit, beside the mixer's cache)
 the block is built with (layer norms with weight and bias, or RMS norms); the gates read the sublayer's own input before
 the convolution.  A sublayer's last product adds into a 32-bit row buffer of the pass; one kernel then gates and norms
 that result into the stream, clears the buffer and leaves the updated stream in the run's type for the products that
-read it next (the gate's, the feed-forward's, the next block's).  In a step in which every sequence brings one token
-the token input, its norm and the mix over the levels are one kernel (a CTA per token).  The stream, the gates' logits and sigmoid, the norms,
+read it next (the gate's, the feed-forward's, the next block's); the last such kernel of a layer also files the layer's
+result as a level and leaves the mix over the levels as the stream.  The stream, the gates' logits and sigmoid, the norms,
 the convolution with its state and the mix over the levels are 32-bit in both precisions."""
 from __future__ import annotations
 
@@ -166,10 +166,14 @@ class GatedResidualBlock(Block):
         stages = ["mixer"] + (["feed_forward"] if self.feed_forward is not None else []) + (["side"] if self.side_dim else [])
 
         def cast_behind(stage: str):
-            """Where the kernel that ends ``stage`` leaves the updated stream in the run's type (None: nowhere)."""
-            if stage != stages[-1]:
-                return ctx.empty((T, h), ctx.dtype)
-            return last if self.depth is None else None    # (the mix over the levels follows and leaves it itself)
+            """Where the kernel that ends ``stage`` leaves the updated stream in the run's type."""
+            return ctx.empty((T, h), ctx.dtype) if stage != stages[-1] else last
+
+        def mix_behind(stage: str) -> dict:
+            """The layer's last kernel also files the layer's result as a level and leaves the mix over the levels."""
+            if self.depth is None or stage != stages[-1]:
+                return {}
+            return dict(levels=levels, n=self.depth[0] + 1, coefficients=self.depth_mix)
 
         read = x
         if self.taps:
@@ -178,7 +182,7 @@ class GatedResidualBlock(Block):
             ops.causal_conv(residual, self.conv_weight, state, ctx.slots_dev, ctx.seq_ids, ctx.cu_seqlens, read, h,
                             add_input=True, update_state=bool(writes_cache) and self.taps > 1)
         self.mixer.forward(read, ctx, mixer_cache, y, writes_cache)
-        x = self._join(y, x, 0, self.mixer_norm, residual, ctx, cast=cast_behind("mixer"))
+        x = self._join(y, x, 0, self.mixer_norm, residual, ctx, cast=cast_behind("mixer"), **mix_behind("mixer"))
         if self.feed_forward is not None:
             y_bias = None
             if hasattr(self.feed_forward, "result_bias"):    # (its last bias joins in the kernel that reads the result anyway)
@@ -186,35 +190,25 @@ class GatedResidualBlock(Block):
                 y_bias = self.feed_forward.result_bias()
             else:
                 self.feed_forward.forward(x, ctx, y)
-            x = self._join(y, x, 1, self.feed_forward_norm, residual, ctx, y_bias=y_bias, cast=cast_behind("feed_forward"))
-        if self.side_dim and ctx.all_decode and ops.token_side_step_fits(h, self.side_dim):
-            # a step of one token per sequence: the token input, its norm and the mix over the levels in one kernel
-            run = self.side_gate.weight.dtype
-            ops.token_side_step(residual, ctx.tokens, self.side_table, self.side_gate.weight, self.side_proj.weight, self.side_norm,
-                                self.side_eps, self.side_dim, levels=levels, n=self.depth[0] + 1 if self.depth is not None else 0,
-                                coefficients=self.depth_mix if self.depth is not None else None,
-                                cast=last if last.dtype == run else None)
-            if last.dtype != run:
-                ops.cast_rows(residual, last)
-            return StreamRows(last)
+            x = self._join(y, x, 1, self.feed_forward_norm, residual, ctx, y_bias=y_bias, cast=cast_behind("feed_forward"),
+                           **mix_behind("feed_forward"))
         if self.side_dim:
             a = self.side_gate.store(x, ctx.dtype, ctx.empty)
             g = ctx.empty((T, self.side_k), ctx.dtype)
             ops.token_gate_rows(a, ctx.tokens, self.side_table, g, self.side_dim)
             self.side_proj.add_to(g, y)
-            ops.gated_norm_step(y, self.side_norm, None, residual, self.side_eps, center=False, cast=cast_behind("side"))
-        if self.depth is not None:
-            ops.depth_average(levels, self.depth[0] + 1, self.depth_mix, residual, cast=last)
+            ops.gated_norm_step(y, self.side_norm, None, residual, self.side_eps, center=False, cast=cast_behind("side"),
+                                **mix_behind("side"))
         return StreamRows(last)
 
-    def _join(self, y, x, which: int, norm, residual, ctx: StepContext, y_bias=None, cast=None):
+    def _join(self, y, x, which: int, norm, residual, ctx: StepContext, y_bias=None, cast=None, **mix):
         """The sublayer's result ``y`` times its gate (a product over the sublayer's input ``x``), normed, into the
         stream; returns ``cast``, which then holds the updated stream in the run's type."""
         bias = getattr(norm, "bias", None)
         w = norm.weight if norm.weight.dtype == torch.float32 else norm.group_form()[0]
         r = self.gates[which].store(x, torch.float32, ctx.empty)    # (the gate's logits leave their product in 32 bits)
         ops.gated_norm_step(y, w, bias, residual, norm.eps, gate=r, gate_bias=self.gate_biases[which], y_bias=y_bias, cast=cast,
-                            center=bias is not None)
+                            center=bias is not None, **mix)
         return cast
 
 

@@ -81,6 +81,28 @@ def test_mix_over_the_levels(dtype, rows, dim, levels):
 
 
 @DTYPES
+@pytest.mark.parametrize("rows, dim, n", [(5, 48, 1), (3, 640, 4), (9, 50, 3), (2, 8448, 2)])
+def test_last_step_of_a_layer_files_its_level_and_mixes(dtype, rows, dim, n):
+    """The norm-and-add kernel with levels: what it leaves equals the plain step followed by the plain mix."""
+    from gpullama3.java_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(rows + dim + n)
+    x, y = torch.randn(rows, dim, generator=g) * 4, torch.randn(rows, dim, generator=g)
+    w, c = torch.randn(dim, generator=g), torch.randn(n + 1, generator=g)
+    kept = torch.randn(n + 2, rows, dim, generator=g)
+    levels = kept.to(DEV)
+    xd, yd = x.to(DEV), y.to(DEV)
+    cast = torch.empty((rows, dim), dtype=dtype, device=DEV)
+    ops.gated_norm_step(yd, w.to(DEV), None, xd, 1e-5, center=False, cast=cast, levels=levels, n=n, coefficients=c.to(DEV))
+    newest = x.to(F) + P.over_root_mean_square(y.to(F), 1e-5) * w.to(F)
+    ref = P.depth_average([kept[j].to(F) for j in range(n)] + [newest], c.to(F))
+    _close(xd, ref, torch.float32, "stream", f32=1e-5)
+    _close(levels[n], newest, torch.float32, "level", f32=1e-5)
+    assert torch.equal(levels[n + 1].cpu(), kept[n + 1]) and torch.equal(levels[:n].cpu(), kept[:n])
+    assert torch.equal(cast.float().cpu(), xd.cpu().to(dtype).float()) and float(yd.abs().max()) == 0.0
+
+
+@DTYPES
 @pytest.mark.parametrize("rows, n, width, columns", [(5, 12, 16, 36), (3, 5, 8, 5), (70, 40, 40, 200), (2, 1, 8, 3)])
 def test_token_gate(dtype, rows, n, width, columns):
     from gpullama3.java_b200.kernels import ops
