@@ -68,7 +68,18 @@ BISUDRA_D = {
         {"type": "attention", "mixer": _att(4, 2, 64, 128, 0.12, 0.25, window=33, rot=(500.0, 64)), "mlp": _moe(128, 4, 2)},
     ],
 }
-CONFIGS = {"A": BISUDRA_A, "B": BISUDRA_B, "C": BISUDRA_C, "D": BISUDRA_D}
+# sizes off every kernel's grid of fast cases: a width and head sizes that are no multiples of 8, sixteen and twenty-four
+# maps on one kv head, as many kv heads as heads, values wider than two maps, every expert chosen, five taps
+BISUDRA_E = {
+    "architecture": "Bisudra", "vocab": 77, "width": 50, "norm": {"eps": 1e-5}, "canon": {"taps": 5},
+    "token_side": {"dim": 3}, "initializer_range": 0.1,
+    "layers": [
+        {"type": "attention", "mixer": _att(8, 1, 12, 10, 0.21, 0.55, window=50, rot=(1000.0, 6)), "mlp": _dense(30)},
+        {"type": "attention", "mixer": _att(12, 1, 6, 20, 0.33, 0.15), "mlp": _moe(10, 5, 5)},
+        {"type": "attention", "mixer": _att(5, 5, 32, 72, 0.1, 0.45, window=300, rot=(10000.0, 32)), "mlp": None},
+    ],
+}
+CONFIGS = {"A": BISUDRA_A, "B": BISUDRA_B, "C": BISUDRA_C, "D": BISUDRA_D, "E": BISUDRA_E}
 
 
 ROUTER_BIAS_STD = 1.0

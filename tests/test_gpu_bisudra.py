@@ -22,7 +22,7 @@ LENGTHS = [1, 2, 33, 64, 65, 131, 40, 200, 70, 260]
 DTYPES = pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def setup(request, session_tmp):
     d = make_bisudra_dir(session_tmp, CONFIGS[request.param], seed=11)
     cfg, weights = plain_inputs(d)
