@@ -44,7 +44,33 @@ struct GatedNormArgs {
     size_t level_stride;    // the stream (and in xc) is sum_(j <= n) c[j] level[j], as depth_average does it
     int n;
     const float* c;         // [n + 1]
+    // not null: a step in which every sequence brings one token also reads for the next block's mixer, a convolution
+    // over time on the stream as it is left: read = h + sum_j conv_w[:, j] h_(t - taps + 1 + j), the older inputs from
+    // conv_state[slots[t]] ([taps - 1][dim], oldest first), which moves on by this token when conv_update
+    const float* conv_w;    // [dim][taps]
+    float* conv_state;
+    size_t slot_stride;
+    const int* slots;       // [T]
+    int taps, conv_update;
+    void* read;             // [T][dim] in xc's type
 };
+
+// The next reader's convolution for one number of token t (sums run from the oldest tap to the newest, then the input
+// itself, as the convolution kernels do).
+template <typename TC>
+__device__ __forceinline__ void read_ahead(const GatedNormArgs& a, int t, int i, float v) {
+    float* st = a.conv_state + (size_t)a.slots[t] * a.slot_stride + i;
+    const float* w = a.conv_w + (size_t)i * a.taps;
+    float acc = 0.f;
+    for (int m = 0; m + 1 < a.taps; ++m) {
+        const float older = st[(size_t)m * a.dim];
+        acc += w[m] * older;
+        if (a.conv_update && m > 0) st[(size_t)(m - 1) * a.dim] = older;
+    }
+    if (a.conv_update && a.taps > 1) st[(size_t)(a.taps - 2) * a.dim] = v;
+    acc += w[a.taps - 1] * v;
+    ((TC*)a.read)[(size_t)t * a.dim + i] = from_f32<TC>(acc + v);
+}
 
 // The mix over the levels for one number: files `value` as level n, returns sum_j c[j] level[j] (j in order).
 __device__ __forceinline__ float mix_levels(const GatedNormArgs& a, size_t at, float value) {
@@ -105,6 +131,7 @@ gated_norm_step_kernel(GatedNormArgs a) {
         xr[i] = v;
         yr[i] = 0.f;
         if (xc) xc[i] = from_f32<TC>(v);
+        if (a.conv_w) read_ahead<TC>(a, t, i, v);
     };
     if (NV > 0) {
 #pragma unroll
@@ -208,6 +235,12 @@ gated_norm_step_vec_kernel(GatedNormArgs a) {
         store4<float>(xr + i, v);
         store4<float>(yr + i, make_float4(0.f, 0.f, 0.f, 0.f));
         if (xc) store4<TC>(xc + i, v);
+        if (a.conv_w) {
+            read_ahead<TC>(a, t, i, v.x);
+            read_ahead<TC>(a, t, i + 1, v.y);
+            read_ahead<TC>(a, t, i + 2, v.z);
+            read_ahead<TC>(a, t, i + 3, v.w);
+        }
     }
 }
 
@@ -312,15 +345,20 @@ static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t 
 // `center` 1: x += layer norm of the gated result (w, b); 0: x += w * z / rms(z) (b ignored).  `r` null: no gate.
 // `r_dtype`: the gate logits' type; `dtype`: that of xc.  `levels` not null: the new x is filed as level `n` of
 // levels [> n][level_stride] and the stream becomes sum_(j <= n) c[j] level[j] (c on the device), as b200_depth_average does it.
+// `conv_w` not null (a step of one token per sequence): `read` receives what the next block's mixer reads (GatedNormArgs).
 extern "C" int b200_gated_norm_step(float* y, const float* y_bias, const void* r, int ld_r, int r_dtype, const float* r_bias,
                                     const float* w, const float* b, float* x, void* xc, int dtype, int n_tokens, int dim,
                                     float eps, int center, float* levels, long long level_stride, int n, const float* c,
-                                    cudaStream_t stream) {
+                                    const float* conv_w, float* conv_state, long long slot_stride, const int* slots, int taps,
+                                    int conv_update, void* read, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dim < 1 || !y || !w || !x || (r && ld_r < dim)) return b200::kErrBadArgument;
     if (levels && (n < 0 || !c || level_stride < (long long)n_tokens * dim)) return b200::kErrBadArgument;
+    if (conv_w && (!read || !slots || taps < 1 || (taps > 1 && (!conv_state || slot_stride < (long long)(taps - 1) * dim))))
+        return b200::kErrBadArgument;
     const b200::GatedNormArgs a = {y, y_bias, r, ld_r, r_bias, w, center ? b : nullptr, x, xc, dim, eps, center ? 1 : 0,
-                                   levels, (size_t)(levels ? level_stride : 0), n, c};
+                                   levels, (size_t)(levels ? level_stride : 0), n, c,
+                                   conv_w, conv_state, (size_t)slot_stride, slots, taps, conv_update, read};
     B200_DISPATCH_DTYPE(r_dtype, TR, B200_DISPATCH_DTYPE2(dtype, TC, return b200::launch_gated_norm<TR, TC>(a, n_tokens, stream)));
     return 0;
 }

@@ -121,7 +121,7 @@ _SIGNATURES = {
                                                 c_float, c_float]),
     "b200_gated_norm_step": ("gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, ctypes.c_longlong, c_int,
-                                                c_void_p]),
+                                                c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_void_p]),
     "b200_depth_average": ("gated_residual", [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               ctypes.c_longlong]),
     "b200_cast_rows": ("gated_residual", [c_void_p, c_void_p, c_int, ctypes.c_longlong]),
@@ -974,11 +974,16 @@ def differential_heads(maps: torch.Tensor, gate: torch.Tensor | None, out: torch
 def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, x: torch.Tensor, eps: float, *,
                     gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None,
                     y_bias: torch.Tensor | None = None, cast: torch.Tensor | None = None, center: bool = True,
-                    levels: torch.Tensor | None = None, n: int = 0, coefficients: torch.Tensor | None = None) -> None:
+                    levels: torch.Tensor | None = None, n: int = 0, coefficients: torch.Tensor | None = None,
+                    read=None) -> None:
     """z = (y (+ y_bias)) * sigmoid(gate (+ gate_bias)); x <- x + layer_norm(z) * weight + bias (``center`` False: x <- x +
     weight * z / rms(z)); y <- 0; ``cast`` receives the new x in its own type.  x, y [T, dim], the vectors float32;
     ``gate`` [T, >= dim], float32 or bfloat16 (None: no gate).  With ``levels`` (float32 [> n, T, dim]) the new x is filed as
-    level ``n`` and what stays as the stream (and in ``cast``) is sum_(j <= n) coefficients[j] levels[j], as ``depth_average``."""
+    level ``n`` and what stays as the stream (and in ``cast``) is sum_(j <= n) coefficients[j] levels[j], as ``depth_average``.
+    ``read`` = (conv_weight float32 [dim, taps], conv_state float32 [slots, >= (taps - 1) * dim], slots int32 [T], update,
+    out [T, dim]) in a step in which every sequence brings one token: ``out`` receives the stream as it is left plus a
+    convolution over time on it, h + sum_j conv_weight[:, j] h_(t - taps + 1 + j), the older inputs from the state at
+    ``slots[t]`` (oldest first), which moves on by this token with ``update``: what the next block's mixer reads."""
     _dev(y, weight, bias, x, gate, gate_bias, y_bias, cast)
     T, dim = x.shape
     assert x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
@@ -990,12 +995,25 @@ def gated_norm_step(y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
         _dev(levels, coefficients)
         assert levels.dtype == coefficients.dtype == torch.float32 and levels.is_contiguous() and coefficients.is_contiguous()
         assert levels.shape[0] > n >= 0 and tuple(levels.shape[1:]) == (T, dim) and coefficients.numel() == n + 1
+    conv = (None, None, 0, None, 0, 0, None)
+    out_type = cast.dtype if cast is not None else None
+    if read is not None:
+        conv_w, conv_state, slots, update, out = read
+        _dev(conv_w, conv_state, slots, out)
+        taps = conv_w.shape[1]
+        assert conv_w.dtype == conv_state.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == dim
+        assert conv_state.stride(1) == 1 and (taps < 2 or conv_state.shape[1] >= (taps - 1) * dim)
+        assert slots.dtype == torch.int32 and slots.numel() == T and out.is_contiguous() and out.shape == x.shape
+        assert out_type is None or out_type == out.dtype
+        out_type = out.dtype
+        conv = (conv_w.data_ptr(), conv_state.data_ptr(), conv_state.stride(0), slots.data_ptr(), taps, 1 if update else 0,
+                out.data_ptr())
     ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_gated_norm_step")(y.data_ptr(), ptr(y_bias), ptr(gate), gate.stride(0) if gate is not None else 0,
                                        dtype_code(gate.dtype) if gate is not None else F32, ptr(gate_bias), weight.data_ptr(),
-                                       ptr(bias), x.data_ptr(), ptr(cast), dtype_code(cast.dtype) if cast is not None else F32,
+                                       ptr(bias), x.data_ptr(), ptr(cast), dtype_code(out_type) if out_type is not None else F32,
                                        T, dim, float(eps), 1 if center else 0, ptr(levels),
-                                       levels.stride(0) if levels is not None else 0, int(n), ptr(coefficients), _stream()),
+                                       levels.stride(0) if levels is not None else 0, int(n), ptr(coefficients), *conv, _stream()),
            "gated_norm_step")
 
 

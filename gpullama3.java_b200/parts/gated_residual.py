@@ -16,7 +16,8 @@ the block is built with (layer norms with weight and bias, or RMS norms); the ga
 the convolution.  A sublayer's last product adds into a 32-bit row buffer of the pass; one kernel then gates and norms
 that result into the stream, clears the buffer and leaves the updated stream in the run's type for the products that
 read it next (the gate's, the feed-forward's, the next block's); the last such kernel of a layer also files the layer's
-result as a level and leaves the mix over the levels as the stream.  The stream, the gates' logits and sigmoid, the norms,
+result as a level and leaves the mix over the levels as the stream, and in a step in which every sequence brings one
+token it applies the next block's input convolution too (that block then launches none).  The stream, the gates' logits and sigmoid, the norms,
 the convolution with its state and the mix over the levels are 32-bit in both precisions."""
 from __future__ import annotations
 
@@ -26,7 +27,7 @@ from ..cache.sequence_cache import EntryNeeds, StateNeed
 from ..config.base import ConfigError
 from ..kernels import ops
 from ..weights.loader import ParamSpec
-from .base import Block, StepContext, all_parts, register_block
+from .base import Block, FirstRead, StepContext, all_parts, register_block
 from .linear import Linear
 
 SUBLAYER_RESULT = "gated residual sublayer result"   # in a pass's ``ctx.extras``: float32 [T, width], zero between uses
@@ -34,14 +35,39 @@ DEPTH_LEVELS = "gated residual depth levels"         # float32 [levels, T, width
 
 
 class StreamRows:
-    """What a block hands the next one: the residual stream as it now stands, in the run's type."""
+    """What a block hands the next one: the residual stream as it now stands, in the run's type; ``read``: what the next
+    block's mixer reads (its convolution applied, its state moved on), when this block's last kernel did that too."""
 
-    def __init__(self, data: torch.Tensor):
-        self.data = data
+    def __init__(self, data: torch.Tensor, read: torch.Tensor | None = None):
+        self.data, self.read = data, read
+
+
+class NoNorm:
+    """What the block answers when asked for its first norm: it has none (its sublayers read the stream itself), but it
+    takes part in the hand-over between blocks, which is keyed on that question."""
+
+    def row_factor_form(self):
+        return None
+
+
+class ReadAhead:
+    """``then_norm`` of a block whose successor offered its first read (a ``FirstRead``): no norm, only the read."""
+
+    def __init__(self, read: FirstRead):
+        self.read = read
+
+    def row_factor_form(self):
+        return None
 
 
 def _pad8(n: int) -> int:
     return -(-n // 8) * 8
+
+
+def ctx_free_shape(read: FirstRead, width: int) -> bool:
+    """Whether a first read is a convolution over rows of ``width`` numbers with 32-bit weights and state."""
+    return (read.weight.dim() == 2 and read.weight.shape[0] == width and read.weight.dtype == torch.float32
+            and read.state.dtype == torch.float32)
 
 
 class GatedResidualBlock(Block):
@@ -137,6 +163,25 @@ class GatedResidualBlock(Block):
         """The block takes the stream in the run's type from the block before it (``x_in``) and leaves it for the next."""
         return True
 
+    def first_norm(self):
+        return NoNorm()
+
+    def first_read(self, ctx: StepContext, cache, writes_cache: bool):
+        """In a step in which every sequence brings one token all older inputs of the convolution come from the state:
+        the block before may then read for this block's mixer in its own last kernel."""
+        if not (self.taps and ctx.all_decode):
+            return None
+        inputs = cache.get("inputs") if isinstance(cache, dict) else None
+        if self.taps > 1 and inputs is None:
+            return None
+        state = inputs.data if self.taps > 1 else self.conv_weight.view(1, -1)
+        return FirstRead(self.conv_weight, state, bool(writes_cache))
+
+    def with_read(self, then_norm, read):
+        if read is None or not ctx_free_shape(read, self.hidden_size):
+            return then_norm
+        return ReadAhead(read) if isinstance(then_norm, NoNorm) else then_norm
+
     # ---- one run
     def forward(self, residual, ctx: StepContext, cache, writes_cache=True, x_in=None, then_norm=None):
         T, h = residual.shape
@@ -170,13 +215,24 @@ class GatedResidualBlock(Block):
             return ctx.empty((T, h), ctx.dtype) if stage != stages[-1] else last
 
         def mix_behind(stage: str) -> dict:
-            """The layer's last kernel also files the layer's result as a level and leaves the mix over the levels."""
-            if self.depth is None or stage != stages[-1]:
+            """The layer's last kernel also files the layer's result as a level and leaves the mix over the levels, and
+            in a step of one token per sequence reads for the next block's mixer."""
+            if stage != stages[-1]:
                 return {}
-            return dict(levels=levels, n=self.depth[0] + 1, coefficients=self.depth_mix)
+            more = dict(read=ahead) if ahead is not None else {}
+            if self.depth is not None:
+                more.update(levels=levels, n=self.depth[0] + 1, coefficients=self.depth_mix)
+            return more
 
+        ahead = None      # the next block's mixer input, if this block's last kernel is to make it
+        if isinstance(then_norm, ReadAhead) and ctx.all_decode:
+            r = then_norm.read
+            ahead = (r.weight, r.state, ctx.slots_dev, r.writes and r.weight.shape[1] > 1,
+                     torch.empty((T, h), dtype=ctx.dtype, device=residual.device))
         read = x
-        if self.taps:
+        if self.taps and isinstance(x_in, StreamRows) and x_in.read is not None:
+            read = x_in.read     # (the block before this one has read for it: convolved, the state moved on)
+        elif self.taps:
             read = ctx.empty((T, h), ctx.dtype)
             state = inputs.data if self.taps > 1 else self.conv_weight.view(1, -1)   # (one tap reads no earlier input)
             ops.causal_conv(residual, self.conv_weight, state, ctx.slots_dev, ctx.seq_ids, ctx.cu_seqlens, read, h,
@@ -199,7 +255,7 @@ class GatedResidualBlock(Block):
             self.side_proj.add_to(g, y)
             ops.gated_norm_step(y, self.side_norm, None, residual, self.side_eps, center=False, cast=cast_behind("side"),
                                 **mix_behind("side"))
-        return StreamRows(last)
+        return StreamRows(last, ahead[4] if ahead is not None else None)
 
     def _join(self, y, x, which: int, norm, residual, ctx: StepContext, y_bias=None, cast=None, **mix):
         """The sublayer's result ``y`` times its gate (a product over the sublayer's input ``x``), normed, into the

@@ -149,6 +149,33 @@ def test_recorded_and_unrecorded_decode_steps_agree(setup, dtype):
     assert float((outs[0] - outs[1]).abs().max()) <= 1e-5 * float(outs[0].abs().max())
 
 
+def test_decode_steps_read_in_the_step_kernel(session_tmp):
+    """In a step of one token per sequence a layer's last kernel applies the next block's input convolution: only the
+    first block launches one; a layer is one kernel per sublayer result, and the mix over the levels has none of its own
+    behind level 0."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+    from gpullama3.java_b200.kernels import ops
+
+    d = make_bisudra_dir(session_tmp, CONFIGS["A"], seed=11)
+    model = load_model(d, torch.bfloat16)
+    cache = model.new_cache(64 * 4)
+    step = StepFunction(model, cache, use_graphs=False)
+    slots = [cache.acquire(), cache.acquire()]
+    step([SequenceInput(slots[0], [5, 6, 7], []), SequenceInput(slots[1], [8], [])])
+    ops.profile_start()
+    step([SequenceInput(s, [9], [0]) for s in slots])
+    table = ops.profile_stop()
+    layers = CONFIGS["A"]["layers"]
+    assert table["b200_causal_conv"][0] == 1
+    assert table["b200_depth_average"][0] == 1
+    assert table["b200_gated_norm_step"][0] == sum(2 + (L["mlp"] is not None) for L in layers)    # mixer, feed-forward, token input
+    assert "b200_cast_rows" not in table
+    ops.profile_start()
+    step([SequenceInput(slots[0], [9, 3], [1]), SequenceInput(slots[1], [4], [0])])     # a portion: every block reads for itself
+    assert ops.profile_stop()["b200_causal_conv"][0] == len(layers)
+
+
 @DTYPES
 def test_logits_do_not_depend_on_the_batch(setup, dtype):
     """A request's logits in a batch of unequal requests are those it has alone, within the rounding of one product (the

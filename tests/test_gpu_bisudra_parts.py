@@ -182,6 +182,7 @@ SHAPES = [  # hidden, heads, kv heads, dim per map, value dim, scale, diff, wind
     (64, 2, 2, 64, 128, 0.125, 0.2, 65, (1e6, 64)),
     (48, 8, 1, 8, 8, 0.5, 0.6, 3, (10.0, 2)),
     (56, 1, 1, 40, 56, 0.2, 0.1, 129, (100.0, 20)),
+    (64, 2, 1, 72, 200, 0.1, 0.3, 70, (1e4, 36)),      # rows of 208 numbers: wider than any tensor-core attention kernel takes
 ]
 
 
