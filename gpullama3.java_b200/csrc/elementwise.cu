@@ -105,6 +105,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 differential_heads_kernel(const T* __restrict__ maps, const T* __restrict__ gate, int ld_gate, T* __restrict__ out,
                           int n_heads, int d, int d_pad, int n_rows, float lambda, float post, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= n_rows) return;
     const int t = row / n_heads, h = row % n_heads;
@@ -187,8 +189,7 @@ extern "C" int b200_differential_heads(const void* maps, const void* gate, int l
     const long long rows = (long long)n_tokens * n_heads;
     if (rows > 0x7fffffffLL) return b200::kErrUnsupportedSize;
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::differential_heads_kernel<T><<<(int)((rows + 3) / 4), 128, 0, stream>>>((const T*)maps, (const T*)gate, ld_gate,
-                                                                                      (T*)out, n_heads, d, d_pad, (int)rows,
-                                                                                      lambda, post, eps));
-    return b200::launch_status();
+        return b200::launch_pdl(b200::differential_heads_kernel<T>, dim3((int)((rows + 3) / 4)), dim3(128), 0, stream,
+                                (const T*)maps, (const T*)gate, ld_gate, (T*)out, n_heads, d, d_pad, (int)rows, lambda, post, eps));
+    return 0;
 }

@@ -12,6 +12,7 @@
 //   bias_act_rows      u <- act(u + bias) in place on a product's result; act: the square of max(., 0)
 //   token_gate_rows    g[t, j] = gelu_tanh(a[t, j]) * table[token[t], j]: a few numbers per token id that the stream gates
 //
+// Every kernel here is launched with programmatic dependent launch and waits for its predecessor before it touches memory.
 // A CTA per token row for the three steps: a thread keeps its share of the row (the elements tid, tid + 256, ...) in
 // registers between the one fetch and the one store when the row has at most 256 * 32 numbers; longer rows are
 // evaluated again in each pass.  Mean and variance are two sums over the same kept values (the variance is the mean of
@@ -85,6 +86,8 @@ template <typename TR, typename TC, int NV>
 __global__ void __launch_bounds__(kStepThreads)
 gated_norm_step_kernel(GatedNormArgs a) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x, dim = a.dim;
     float* yr = a.y + (size_t)t * dim;
     float* xr = a.x + (size_t)t * dim;
@@ -168,6 +171,8 @@ template <typename TR, typename TC, int NV>
 __global__ void __launch_bounds__(kStepThreads)
 gated_norm_step_vec_kernel(GatedNormArgs a) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x, dim = a.dim;
     float* yr = a.y + (size_t)t * dim;
     float* xr = a.x + (size_t)t * dim;
@@ -250,6 +255,8 @@ template <typename TR>
 __global__ void __launch_bounds__(256)
 depth_average_vec_kernel(float* __restrict__ levels, size_t level_stride, int n, const float* __restrict__ c,
                          float* __restrict__ x, TR* __restrict__ xc, size_t total4) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (size_t)gridDim.x * blockDim.x) {
         const size_t i = q * 4;
         const float4 newest = load4<float>(x + i);
@@ -271,6 +278,8 @@ template <typename TR>
 __global__ void __launch_bounds__(256)
 depth_average_kernel(float* __restrict__ levels, size_t level_stride, int n, const float* __restrict__ c,
                      float* __restrict__ x, TR* __restrict__ xc, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const float newest = x[i];
         levels[(size_t)n * level_stride + i] = newest;
@@ -285,6 +294,8 @@ depth_average_kernel(float* __restrict__ levels, size_t level_stride, int n, con
 template <typename TR>
 __global__ void __launch_bounds__(256)
 cast_rows_kernel(const float* __restrict__ x, TR* __restrict__ xc, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         xc[i] = from_f32<TR>(x[i]);
 }
@@ -292,6 +303,8 @@ cast_rows_kernel(const float* __restrict__ x, TR* __restrict__ xc, size_t total)
 template <typename TR>
 __global__ void __launch_bounds__(256)
 bias_act_rows_kernel(TR* __restrict__ u, int ld, const float* __restrict__ bias, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     TR* ur = u + (size_t)blockIdx.x * ld;
     for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < n; e += gridDim.y * blockDim.x) {
         const float z = fmaxf(to_f32<TR>(ur[e]) + (bias ? bias[e] : 0.f), 0.f);
@@ -304,6 +317,8 @@ template <typename TR, typename TT>
 __global__ void __launch_bounds__(128)
 token_gate_rows_kernel(const TR* __restrict__ a, int ld_a, const int* __restrict__ tokens, const TT* __restrict__ table,
                        int ld_table, int n_rows_table, TR* __restrict__ g, int ld_g, int n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= n_rows_table ? n_rows_table - 1 : tok);
@@ -319,16 +334,17 @@ static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t 
                           (uintptr_t)a.r_bias | (uintptr_t)a.r | (uintptr_t)a.xc | (uintptr_t)a.levels;
     if (a.dim % 4 == 0 && a.ld_r % 4 == 0 && (all & 15) == 0 && a.level_stride % 4 == 0 && a.dim <= 32 * kStepThreads) {
         const int per4 = (a.dim / 4 + kStepThreads - 1) / kStepThreads;
-#define B200_GATED_NORM_VEC(NV) gated_norm_step_vec_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
+#define B200_GATED_NORM_VEC(NV) \
+    return launch_pdl(gated_norm_step_vec_kernel<TR, TC, NV>, dim3(n_tokens), dim3(kStepThreads), 0, stream, a)
         if (per4 <= 1) B200_GATED_NORM_VEC(1);
         else if (per4 <= 2) B200_GATED_NORM_VEC(2);
         else if (per4 <= 4) B200_GATED_NORM_VEC(4);
         else B200_GATED_NORM_VEC(8);
 #undef B200_GATED_NORM_VEC
-        return launch_status();
     }
     const int per = (a.dim + kStepThreads - 1) / kStepThreads;
-#define B200_GATED_NORM_CASE(NV) gated_norm_step_kernel<TR, TC, NV><<<n_tokens, kStepThreads, 0, stream>>>(a)
+#define B200_GATED_NORM_CASE(NV) \
+    return launch_pdl(gated_norm_step_kernel<TR, TC, NV>, dim3(n_tokens), dim3(kStepThreads), 0, stream, a)
     if (per <= 1) B200_GATED_NORM_CASE(1);
     else if (per <= 2) B200_GATED_NORM_CASE(2);
     else if (per <= 4) B200_GATED_NORM_CASE(4);
@@ -337,7 +353,6 @@ static int launch_gated_norm(const GatedNormArgs& a, int n_tokens, cudaStream_t 
     else if (per <= 32) B200_GATED_NORM_CASE(32);
     else B200_GATED_NORM_CASE(0);
 #undef B200_GATED_NORM_CASE
-    return launch_status();
 }
 
 }  // namespace b200
@@ -372,23 +387,24 @@ extern "C" int b200_depth_average(float* levels, long long level_stride, int n, 
         const long long blocks4 = (total / 4 + 255) / 256;
         const int grid4 = (int)(blocks4 < 148 * 16 ? blocks4 : 148 * 16);
         B200_DISPATCH_DTYPE(dtype, T,
-            b200::depth_average_vec_kernel<T><<<grid4, 256, 0, stream>>>(levels, (size_t)level_stride, n, c, x, (T*)xc,
-                                                                       (size_t)(total / 4)));
-        return b200::launch_status();
+            return b200::launch_pdl(b200::depth_average_vec_kernel<T>, dim3(grid4), dim3(256), 0, stream, levels,
+                                    (size_t)level_stride, n, c, x, (T*)xc, (size_t)(total / 4)));
     }
     const long long blocks = (total + 255) / 256;
     const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::depth_average_kernel<T><<<grid, 256, 0, stream>>>(levels, (size_t)level_stride, n, c, x, (T*)xc, (size_t)total));
-    return b200::launch_status();
+        return b200::launch_pdl(b200::depth_average_kernel<T>, dim3(grid), dim3(256), 0, stream, levels, (size_t)level_stride, n, c,
+                                x, (T*)xc, (size_t)total));
+    return 0;
 }
 
 extern "C" int b200_cast_rows(const float* x, void* xc, int dtype, long long total, cudaStream_t stream) {
     if (total <= 0) return 0;
     const long long blocks = (total + 255) / 256;
     const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
-    B200_DISPATCH_DTYPE(dtype, T, b200::cast_rows_kernel<T><<<grid, 256, 0, stream>>>(x, (T*)xc, (size_t)total));
-    return b200::launch_status();
+    B200_DISPATCH_DTYPE(dtype, T, return b200::launch_pdl(b200::cast_rows_kernel<T>, dim3(grid), dim3(256), 0, stream, x, (T*)xc,
+                                                          (size_t)total));
+    return 0;
 }
 
 // act 0: max(u + bias, 0)^2
@@ -398,8 +414,9 @@ extern "C" int b200_bias_act_rows(void* u, int ld, int dtype, const float* bias,
     if (n_tokens <= 0 || n <= 0) return 0;
     const int ny = (n + 1023) / 1024;
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::bias_act_rows_kernel<T><<<dim3(n_tokens, ny > 64 ? 64 : ny), 256, 0, stream>>>((T*)u, ld, bias, n));
-    return b200::launch_status();
+        return b200::launch_pdl(b200::bias_act_rows_kernel<T>, dim3(n_tokens, ny > 64 ? 64 : ny), dim3(256), 0, stream, (T*)u, ld,
+                                bias, n));
+    return 0;
 }
 
 extern "C" int b200_token_gate_rows(const void* a, int ld_a, int dtype, const int* tokens, const void* table, int table_dtype,
@@ -409,8 +426,8 @@ extern "C" int b200_token_gate_rows(const void* a, int ld_a, int dtype, const in
     if (n < 0 || n > width || ld_g < width || n_rows_table < 1) return b200::kErrBadArgument;
     B200_DISPATCH_DTYPE(dtype, T,
         B200_DISPATCH_DTYPE2(table_dtype, TT,
-            b200::token_gate_rows_kernel<T, TT><<<n_tokens, 128, 0, stream>>>((const T*)a, ld_a, tokens, (const TT*)table, ld_table,
-                                                                             n_rows_table, (T*)g, ld_g, n, width)));
-    return b200::launch_status();
+            return b200::launch_pdl(b200::token_gate_rows_kernel<T, TT>, dim3(n_tokens), dim3(128), 0, stream, (const T*)a, ld_a,
+                                    tokens, (const TT*)table, ld_table, n_rows_table, (T*)g, ld_g, n, width)));
+    return 0;
 }
 
