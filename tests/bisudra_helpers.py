@@ -79,7 +79,17 @@ BISUDRA_E = {
         {"type": "attention", "mixer": _att(5, 5, 32, 72, 0.1, 0.45, window=300, rot=(10000.0, 32)), "mlp": None},
     ],
 }
-CONFIGS = {"A": BISUDRA_A, "B": BISUDRA_B, "C": BISUDRA_C, "D": BISUDRA_D, "E": BISUDRA_E}
+# nothing routed and no convolution: every part lets a short prompt run as a recorded pass padded to a whole page
+BISUDRA_F = {
+    "architecture": "Bisudra", "vocab": 90, "width": 72, "norm": {"eps": 1e-5}, "token_side": {"dim": 9},
+    "initializer_range": 0.09,
+    "layers": [
+        {"type": "attention", "mixer": _att(2, 1, 32, 64, 0.15, 0.35, window=80, rot=(2000.0, 12)), "mlp": _dense(100)},
+        {"type": "attention", "mixer": _att(3, 3, 16, 24, 0.3, 0.65, rot=(700.0, 16)), "mlp": None},
+        {"type": "attention", "mixer": _att(4, 2, 24, 40, 0.2, 0.5, window=31), "mlp": _dense(56)},
+    ],
+}
+CONFIGS = {"A": BISUDRA_A, "B": BISUDRA_B, "C": BISUDRA_C, "D": BISUDRA_D, "E": BISUDRA_E, "F": BISUDRA_F}
 
 
 ROUTER_BIAS_STD = 1.0

@@ -22,7 +22,7 @@ LENGTHS = [1, 2, 33, 64, 65, 131, 40, 200, 70, 260]
 DTYPES = pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "F"])
 def setup(request, session_tmp):
     d = make_bisudra_dir(session_tmp, CONFIGS[request.param], seed=11)
     cfg, weights = plain_inputs(d)
@@ -174,6 +174,13 @@ def test_decode_steps_read_in_the_step_kernel(session_tmp):
     ops.profile_start()
     step([SequenceInput(slots[0], [9, 3], [1]), SequenceInput(slots[1], [4], [0])])     # a portion: every block reads for itself
     assert ops.profile_stop()["b200_causal_conv"][0] == len(layers)
+
+
+def test_which_models_run_short_prompts_as_recorded_passes(session_tmp):
+    from gpullama3.java_b200.engine.trace import load_model
+
+    safe = {name: load_model(make_bisudra_dir(session_tmp, CONFIGS[name], seed=11), torch.bfloat16).pad_safe for name in CONFIGS}
+    assert safe == {"A": False, "B": False, "C": False, "D": False, "E": False, "F": True}
 
 
 @DTYPES
