@@ -64,7 +64,7 @@ def _pad8(n: int) -> int:
     return -(-n // 8) * 8
 
 
-def ctx_free_shape(read: FirstRead, width: int) -> bool:
+def _reads_rows_of(read: FirstRead, width: int) -> bool:
     """Whether a first read is a convolution over rows of ``width`` numbers with 32-bit weights and state."""
     return (read.weight.dim() == 2 and read.weight.shape[0] == width and read.weight.dtype == torch.float32
             and read.state.dtype == torch.float32)
@@ -178,7 +178,7 @@ class GatedResidualBlock(Block):
         return FirstRead(self.conv_weight, state, bool(writes_cache))
 
     def with_read(self, then_norm, read):
-        if read is None or not ctx_free_shape(read, self.hidden_size):
+        if read is None or not _reads_rows_of(read, self.hidden_size):
             return then_norm
         return ReadAhead(read) if isinstance(then_norm, NoNorm) else then_norm
 

@@ -3,7 +3,6 @@ and norms a sublayer's result into the stream, the mix over the levels, the toke
 bias, the rows of two maps laid side by side, the difference of two maps with its norm and gate, differential attention
 as a part alone (prompts, portions and single tokens, with a score made to stand out so that one far key carries the
 result), the dense feed-forward, the router with its bias, and the block alone."""
-import math
 
 import pytest
 import torch
